@@ -1,0 +1,132 @@
+/*
+ * C ABI of the B200 (sm_100a) ring-flash-attention hop kernels.
+ *
+ * This is the drop-in boundary for the sequence-parallel attention operator
+ * `ring_flash_attn(q, k, v, softmax_scale, causal, zigzag, group)` of
+ * AntonotnaWang/opt_ring_flash_attn (optimized_ring_flash_attn.py:1297-1367).
+ * The reference is pure Python + Triton and has no FFI of its own; every entry
+ * point below replaces one Triton kernel launch or torch elementwise op that
+ * the reference's ring schedulers issue once per ring hop, and cites it.
+ *
+ * Rules of the ABI
+ *  - plain pointers and sizes only; all pointers are device pointers unless
+ *    stated otherwise; the library allocates nothing and keeps no pointer
+ *    after a call returns;
+ *  - every call is asynchronous on `stream` (a cudaStream_t passed as void*);
+ *    no call synchronises the device;
+ *  - return value: RFA_OK or a negative RFA_ERR_* code (never an exception,
+ *    abort or trap);
+ *  - `status` points to one int32 in device memory, zero-initialised by the
+ *    caller.  A kernel whose internal pipeline wait runs out of time writes a
+ *    non-zero code there and returns early; later launches that see a non-zero
+ *    status return immediately.  The host reads it whenever it wants to.
+ *
+ * Tensor contract (same as the reference, optimized_ring_flash_attn.py:1346-1360):
+ *  q [B, Sq, Hq, D], k/v [B, Skv, Hkv, D], contiguous, bf16 or fp16,
+ *  Hq % Hkv == 0, D % 8 == 0, D <= 256, q head h uses kv head h / (Hq / Hkv).
+ */
+#ifndef RFA_B200_H_
+#define RFA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RFA_OK 0
+#define RFA_ERR_INVALID_ARG (-1) /* null pointer, non-positive size, Hq % Hkv != 0, ... */
+#define RFA_ERR_UNSUPPORTED (-2) /* head dim not a multiple of 8 or above 256, unknown dtype */
+#define RFA_ERR_CUDA (-3)        /* a CUDA runtime call or the launch failed */
+#define RFA_ERR_DRIVER (-4)      /* the driver rejected a tensor-map descriptor */
+
+#define RFA_DTYPE_BF16 0
+#define RFA_DTYPE_FP16 1
+
+/* Version of this ABI (major * 100 + minor). */
+int rfa_version(void);
+
+/* Rows per sequence tile; per-row statistics (lse, delta) are stored with the
+ * sequence length rounded up to a multiple of this. */
+int rfa_seq_tile(void);
+
+/* Number of fp32 elements of the forward accumulator state for the given shape
+ * (private tiled layout; allocate once per shape, opaque to the caller). */
+size_t rfa_fwd_acc_elems(int B, int Sq, int Hq, int D);
+
+/*
+ * One ring hop of the forward pass: attention of the local queries against one
+ * K/V block, folded into the running fp32 (m, l, acc) state.
+ * Replaces `_native_fwd_step_kernel` (optimized_ring_flash_attn.py:519-615) and
+ * the online-softmax merge `_merge_kernel` (optimized_ring_flash_attn.py:328-417).
+ *
+ *  acc   fp32 [rfa_fwd_acc_elems]        unnormalised output accumulator (state)
+ *  m, l  fp32 [B, Hq, Spad]              running maximum (log2 domain) and sum
+ *  out   dtype [B, Sq, Hq, D]            written only when last != 0
+ *  lse   fp32 [B, Hq, Spad]              natural-log LSE, written only when last != 0
+ *  first != 0: the state is initialised by this hop (not read)
+ *  last  != 0: out and lse are produced (the state is not written)
+ *  causal_diag != 0: the K/V block is the queries' own block; key j is visible
+ *                    to query i iff j <= i.  Otherwise the block is fully visible.
+ *  Spad = Sq rounded up to rfa_seq_tile().
+ */
+int rfa_fwd_hop(const void* q, const void* k, const void* v, float* acc, float* m, float* l, void* out, float* lse,
+                int B, int Sq, int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale, int first, int last,
+                int causal_diag, int* status, void* stream);
+
+/*
+ * Backward preprocessing, once per backward pass:
+ *   delta[b,h,s] = sum_d out[b,s,h,d] * dout[b,s,h,d]
+ *   lse2[b,h,s]  = lse[b,h,s] * log2(e)      (rows s >= Sq: lse2 = +inf, delta = 0)
+ * and, when dq_acc != NULL, dq_acc[B,Sq,Hq,D] (fp32) is cleared.
+ * Replaces `_bwd_preprocess_kernel` (optimized_ring_flash_attn.py:645-669).
+ */
+int rfa_bwd_prepare(const void* out, const void* dout, const float* lse, float* delta, float* lse2, float* dq_acc,
+                    int B, int Sq, int Hq, int D, int dtype, int* status, void* stream);
+
+/*
+ * One ring hop of the backward pass against one K/V block:
+ *   dq_acc[B,Sq,Hq,D] (fp32)  +=  scale * dS  K
+ *   dkdv_out[0] = (accumulate_prev ? dkdv_prev[0] : 0) + scale * dS^T Q
+ *   dkdv_out[1] = (accumulate_prev ? dkdv_prev[1] : 0) + P^T dO
+ * with P = exp2(scale*log2e * Q K^T - lse2), dS = P o (dO V^T - delta).
+ * dkdv_* are fp32 [2, B, Skv, Hkv, D] (the packed buffer that travels round the
+ * ring); dkdv_out may alias dkdv_prev.  dq_acc is updated with fp32 reductions.
+ * Replaces `_bwd_dq_kernel` (optimized_ring_flash_attn.py:672-735),
+ * `_bwd_dkdv_kernel` (optimized_ring_flash_attn.py:738-805) and the accumulate
+ * kernels `_dq_accum_kernel` / `_dkdv_accum_kernel` (optimized_ring_flash_attn.py:441-503).
+ */
+int rfa_bwd_hop(const void* q, const void* k, const void* v, const void* dout, const float* lse2, const float* delta,
+                float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B, int Sq, int Skv, int Hq, int Hkv,
+                int D, int dtype, float softmax_scale, int accumulate_prev, int causal_diag, int* status,
+                void* stream);
+
+/*
+ * dst[i] = (dtype) src[i] for n elements.  Replaces the final `.to(q.dtype)`
+ * casts of the fp32 gradient accumulators (optimized_ring_flash_attn.py:1027-1029).
+ */
+int rfa_cast_from_f32(const float* src, void* dst, size_t n, int dtype, void* stream);
+
+/*
+ * Packs K and V ([B, Skv, Hkv, D] each, `bytes_each` bytes) into one contiguous
+ * [2, B, Skv, Hkv, D] transport buffer.  Replaces `kv_send[0].copy_(k);
+ * kv_send[1].copy_(v)` (optimized_ring_flash_attn.py:836-838, 974-976).
+ */
+int rfa_pack_kv(const void* k, const void* v, void* dst, size_t bytes_each, void* stream);
+
+/*
+ * Diagnostic: one 128x128x128 tensor-core product through each operand path the
+ * hop kernels use (mode 0..4), C fp32 [128,128] row-major, A and B bf16
+ * [128,128] row-major.  Modes: 0 C=A*B^T (both K-major, shared memory);
+ * 1 C=A*B (B MN-major); 2 C=A*B with A staged in tensor memory; 3 C=A^T*B (both
+ * MN-major); 4 as 0 with A written to shared memory by threads.
+ * No counterpart in the reference.
+ */
+int rfa_debug_mma_probe(int mode, const void* a, const void* b, float* c, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* RFA_B200_H_ */

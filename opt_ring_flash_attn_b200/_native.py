@@ -1,0 +1,147 @@
+"""ctypes binding of ``librfa_b200.so`` (the C ABI declared in ``include/rfa_b200.h``).
+
+There is no fallback: if the library is missing or a call fails, a
+``RuntimeError`` is raised.  Tensors are passed as raw device pointers
+(``tensor.data_ptr()``); the stream is the current torch CUDA stream unless
+given.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent / "librfa_b200.so"
+_lib: Optional[ctypes.CDLL] = None
+
+RFA_OK = 0
+ERROR_NAMES = {
+    -1: "RFA_ERR_INVALID_ARG",
+    -2: "RFA_ERR_UNSUPPORTED",
+    -3: "RFA_ERR_CUDA",
+    -4: "RFA_ERR_DRIVER",
+}
+STATUS_NAMES = {0: "ok", 1: "a bounded pipeline wait inside a kernel ran out of time"}
+
+DTYPE_CODES = {torch.bfloat16: 0, torch.float16: 1}
+
+# name -> (restype, argtypes); must list every symbol of include/rfa_b200.h
+_vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+SIGNATURES = {
+    "rfa_version": (_i, []),
+    "rfa_seq_tile": (_i, []),
+    "rfa_fwd_acc_elems": (_sz, [_i, _i, _i, _i]),
+    "rfa_fwd_hop": (_i, [_vp] * 8 + [_i] * 7 + [_f] + [_i] * 3 + [_vp, _vp]),
+    "rfa_bwd_prepare": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp]),
+    "rfa_bwd_hop": (_i, [_vp] * 9 + [_i] * 7 + [_f] + [_i] * 2 + [_vp, _vp]),
+    "rfa_cast_from_f32": (_i, [_vp, _vp, _sz, _i, _vp]),
+    "rfa_pack_kv": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "rfa_debug_mma_probe": (_i, [_i, _vp, _vp, _vp, _vp, _vp]),
+}
+
+
+def library_path() -> Path:
+    return _LIB_PATH
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (building nothing: see ``build.py``)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        raise RuntimeError(
+            f"{_LIB_PATH} is missing: build it with `python -m opt_ring_flash_attn_b200.build` "
+            "(there is no non-CUDA fallback for ring_flash_attn)"
+        )
+    lib = ctypes.CDLL(str(_LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != RFA_OK:
+        raise RuntimeError(f"{what} failed: {ERROR_NAMES.get(rc, rc)}")
+
+
+def _stream(stream: Optional[torch.cuda.Stream]) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def seq_tile() -> int:
+    return 128
+
+
+def padded_seq(s: int) -> int:
+    return (s + 127) // 128 * 128
+
+
+def fwd_acc_elems(B: int, Sq: int, Hq: int, D: int) -> int:
+    n = load().rfa_fwd_acc_elems(B, Sq, Hq, D)
+    if n == 0:
+        raise RuntimeError(f"unsupported shape for the forward state: B={B} S={Sq} H={Hq} D={D}")
+    return n
+
+
+def fwd_hop(q, k, v, acc, m, l, out, lse, softmax_scale: float, first: bool, last: bool, causal_diag: bool,
+            status: torch.Tensor, stream=None) -> None:
+    B, Sq, Hq, D = q.shape
+    _, Skv, Hkv, _ = k.shape
+    rc = load().rfa_fwd_hop(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(acc), _ptr(m), _ptr(l), _ptr(out), _ptr(lse),
+        B, Sq, Skv, Hq, Hkv, D, DTYPE_CODES[q.dtype], float(softmax_scale),
+        int(first), int(last), int(causal_diag), _ptr(status), _stream(stream))
+    _check(rc, "rfa_fwd_hop")
+
+
+def bwd_prepare(out, dout, lse, delta, lse2, dq_acc, status, stream=None) -> None:
+    B, Sq, Hq, D = out.shape
+    rc = load().rfa_bwd_prepare(_ptr(out), _ptr(dout), _ptr(lse), _ptr(delta), _ptr(lse2), _ptr(dq_acc),
+                                B, Sq, Hq, D, DTYPE_CODES[out.dtype], _ptr(status), _stream(stream))
+    _check(rc, "rfa_bwd_prepare")
+
+
+def bwd_hop(q, k, v, dout, lse2, delta, dq_acc, dkdv_prev, dkdv_out, softmax_scale: float, accumulate_prev: bool,
+            causal_diag: bool, status, stream=None) -> None:
+    B, Sq, Hq, D = q.shape
+    _, Skv, Hkv, _ = k.shape
+    rc = load().rfa_bwd_hop(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(dout), _ptr(lse2), _ptr(delta), _ptr(dq_acc), _ptr(dkdv_prev),
+        _ptr(dkdv_out), B, Sq, Skv, Hq, Hkv, D, DTYPE_CODES[q.dtype], float(softmax_scale),
+        int(accumulate_prev), int(causal_diag), _ptr(status), _stream(stream))
+    _check(rc, "rfa_bwd_hop")
+
+
+def cast_from_f32(src: torch.Tensor, dst: torch.Tensor, stream=None) -> None:
+    assert src.dtype == torch.float32 and src.numel() == dst.numel()
+    rc = load().rfa_cast_from_f32(_ptr(src), _ptr(dst), src.numel(), DTYPE_CODES[dst.dtype], _stream(stream))
+    _check(rc, "rfa_cast_from_f32")
+
+
+def pack_kv(k: torch.Tensor, v: torch.Tensor, dst: torch.Tensor, stream=None) -> None:
+    nbytes = k.numel() * k.element_size()
+    rc = load().rfa_pack_kv(_ptr(k), _ptr(v), _ptr(dst), nbytes, _stream(stream))
+    _check(rc, "rfa_pack_kv")
+
+
+def mma_probe(mode: int, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, status: torch.Tensor, stream=None) -> None:
+    rc = load().rfa_debug_mma_probe(mode, _ptr(a), _ptr(b), _ptr(c), _ptr(status), _stream(stream))
+    _check(rc, "rfa_debug_mma_probe")
+
+
+def check_status(status: torch.Tensor, what: str = "ring_flash_attn") -> None:
+    """Read the device status word (synchronises) and raise if a kernel reported a problem."""
+    code = int(status.item())
+    if code != 0:
+        raise RuntimeError(f"{what}: device status {code}: {STATUS_NAMES.get(code, 'unknown')}")

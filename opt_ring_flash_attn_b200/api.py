@@ -1,0 +1,95 @@
+"""Public operator: ``ring_flash_attn(q, k, v, softmax_scale, causal, zigzag, group)``.
+
+Same name, parameter order, defaults, return value and autograd behaviour as the
+reference's entry point (optimized_ring_flash_attn.py:1297-1367): forward saves
+``(q, k, v, out, lse)``, backward returns ``(dq, dk, dv, None, None, None, None)``.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import schedule
+
+_SUPPORTED = (torch.bfloat16, torch.float16)
+
+
+def _validate(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float) -> None:
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("q, k, v must be [B, S_local, H, D]")
+    if q.dtype not in _SUPPORTED or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError(f"q, k, v must share a dtype in {_SUPPORTED}, got {q.dtype}, {k.dtype}, {v.dtype}")
+    if k.shape != v.shape:
+        raise ValueError(f"k and v shapes differ: {tuple(k.shape)} vs {tuple(v.shape)}")
+    B, S, Hq, D = q.shape
+    if k.shape[0] != B or k.shape[1] != S or k.shape[3] != D:
+        raise ValueError(f"q {tuple(q.shape)} and k {tuple(k.shape)} disagree in batch, local sequence or head dim")
+    # same contract as the reference's assert (optimized_ring_flash_attn.py:822)
+    assert Hq % k.shape[2] == 0, "H_q must be a multiple of H_kv"
+    if D > 256 or D % 8 != 0:
+        raise ValueError(f"head_dim must be a multiple of 8 and <= 256, got {D}")
+    if not (softmax_scale > 0):
+        raise ValueError("softmax_scale must be positive")
+    if not q.is_cuda:
+        raise RuntimeError("ring_flash_attn runs on CUDA tensors only (sm_100a kernels; there is no CPU path)")
+
+
+class _RingFlashAttnFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, softmax_scale, causal, zigzag, group):
+        if softmax_scale is None:
+            softmax_scale = q.shape[-1] ** -0.5
+        if zigzag:
+            assert causal, "zigzag mode requires causal=True"
+            raise NotImplementedError("zigzag layout is not available in this build")
+        _validate(q, k, v, softmax_scale)
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out, lse = schedule.ring_forward(group, q, k, v, softmax_scale, causal)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.softmax_scale = softmax_scale
+        ctx.causal = causal
+        ctx.group = group
+        ctx.mark_non_differentiable(lse)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, _dlse=None):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = schedule.ring_backward(ctx.group, dout, q, k, v, out, lse, ctx.softmax_scale, ctx.causal)
+        return dq, dk, dv, None, None, None, None
+
+
+def ring_flash_attn(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    softmax_scale: Optional[float] = None,
+    causal: bool = False,
+    zigzag: bool = False,
+    group: Optional[dist.ProcessGroup] = None,
+) -> torch.Tensor:
+    """Sequence-parallel ring flash attention.
+
+    Args:
+      q:  [B, S_local, H_q, D]   bf16/fp16
+      k:  [B, S_local, H_kv, D]  bf16/fp16 (H_kv may divide H_q: GQA)
+      v:  [B, S_local, H_kv, D]
+      softmax_scale: 1/sqrt(D) by default.
+      causal: causal mask over the full (global) sequence; rank r holds tokens
+              [r*S_local, (r+1)*S_local).
+      zigzag: accepted for signature compatibility; raises NotImplementedError.
+      group:  process group (default: WORLD).  Without an initialised process
+              group the call is plain single-GPU flash attention.
+
+    Returns: out [B, S_local, H_q, D] in q's dtype.
+    """
+    out, _ = _RingFlashAttnFunc.apply(q, k, v, softmax_scale, causal, zigzag, group)
+    return out
+
+
+def ring_flash_attn_with_lse(q, k, v, softmax_scale=None, causal=False, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """As :func:`ring_flash_attn`, also returning the log-sum-exp ``[B, H_q, S_local]`` (fp32, not differentiable)."""
+    out, lse = _RingFlashAttnFunc.apply(q, k, v, softmax_scale, causal, False, group)
+    return out, lse[:, :, : q.shape[1]]

@@ -1,0 +1,216 @@
+// Host utilities (tensor-map factory) and the small bandwidth-bound kernels of
+// the path: backward preprocessing, fp32 -> 16-bit casts, K/V packing.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include <type_traits>
+
+#include "common.h"
+
+namespace rfa {
+
+// cuTensorMapEncodeTiled is reached through the runtime's driver entry point
+// lookup so that the library carries no link-time dependency on libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !ptr) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  return fn;
+}
+
+int make_tmap_bshd(CUtensorMap* out, const void* base, int dtype, int B, int S, int H, int D, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return RFA_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return RFA_ERR_INVALID_ARG;
+  const CUtensorMapDataType dt = (dtype == RFA_DTYPE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t gdim[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(S),
+                        static_cast<cuuint64_t>(B)};
+  cuuint64_t gstride[3] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(H) * D * 2,
+                           static_cast<cuuint64_t>(S) * H * D * 2};
+  cuuint32_t box[4] = {64u, 1u, static_cast<cuuint32_t>(box_rows), 1u};
+  cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  CUresult r = fn(out, dt, 4, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? RFA_OK : RFA_ERR_DRIVER;
+}
+
+// ----------------------------------------------------------------------------
+// Backward preprocessing: one warp per (b, s, h) row.
+//   delta = sum_d out*dout ; lse2 = lse*log2(e) ; optional clear of the fp32 dQ accumulator row.
+// Streams out, dout once (2*B*S*Hq*D*2 bytes) and writes dq_acc once: HBM-bound.
+// ----------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float dot8(const uint4& a, const uint4& b);
+template <>
+__device__ __forceinline__ float dot8<__nv_bfloat16>(const uint4& a, const uint4& b) {
+  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __bfloat1622float2(pa[i]);
+    const float2 y = __bfloat1622float2(pb[i]);
+    s = fmaf(x.x, y.x, s);
+    s = fmaf(x.y, y.y, s);
+  }
+  return s;
+}
+template <>
+__device__ __forceinline__ float dot8<__half>(const uint4& a, const uint4& b) {
+  const __half2* pa = reinterpret_cast<const __half2*>(&a);
+  const __half2* pb = reinterpret_cast<const __half2*>(&b);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __half22float2(pa[i]);
+    const float2 y = __half22float2(pb[i]);
+    s = fmaf(x.x, y.x, s);
+    s = fmaf(x.y, y.y, s);
+  }
+  return s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) bwd_prepare_kernel(const T* __restrict__ out, const T* __restrict__ dout,
+                                                         const float* __restrict__ lse, float* __restrict__ delta,
+                                                         float* __restrict__ lse2, float* __restrict__ dq_acc, int B,
+                                                         int Sq, int Spad, int Hq, int D) {
+  const int lane = threadIdx.x & 31;
+  const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long rows = static_cast<long long>(B) * Spad * Hq;
+  const int vec_per_row = D / 8;  // 16-byte vectors of 16-bit elements
+  for (long long r = warp_global; r < rows; r += nwarps) {
+    // r enumerates (b, s, h) with h fastest so that consecutive warps stream consecutive memory.
+    const int h = static_cast<int>(r % Hq);
+    const long long bs = r / Hq;
+    const int s = static_cast<int>(bs % Spad);
+    const int b = static_cast<int>(bs / Spad);
+    const size_t stat = (static_cast<size_t>(b) * Hq + h) * Spad + s;
+    if (s >= Sq) {
+      if (lane == 0) {
+        delta[stat] = 0.f;
+        lse2[stat] = INFINITY;
+      }
+      continue;
+    }
+    const size_t row_off = ((static_cast<size_t>(b) * Sq + s) * Hq + h) * D;
+    float acc = 0.f;
+    for (int v = lane; v < vec_per_row; v += 32) {
+      const uint4 a = *reinterpret_cast<const uint4*>(out + row_off + v * 8);
+      const uint4 g = *reinterpret_cast<const uint4*>(dout + row_off + v * 8);
+      acc += dot8<T>(a, g);
+    }
+    if (dq_acc != nullptr) {
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int v = lane; v < D / 4; v += 32) *reinterpret_cast<float4*>(dq_acc + row_off + v * 4) = z;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+      delta[stat] = acc;
+      lse2[stat] = lse[stat] * 1.4426950408889634f;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) cast_from_f32_kernel(const float* __restrict__ src, T* __restrict__ dst,
+                                                           size_t n8, size_t n) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    const float4 a = *reinterpret_cast<const float4*>(src + i * 8);
+    const float4 b = *reinterpret_cast<const float4*>(src + i * 8 + 4);
+    T tmp[8];
+    if constexpr (sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value) {
+      tmp[0] = __float2bfloat16_rn(a.x); tmp[1] = __float2bfloat16_rn(a.y);
+      tmp[2] = __float2bfloat16_rn(a.z); tmp[3] = __float2bfloat16_rn(a.w);
+      tmp[4] = __float2bfloat16_rn(b.x); tmp[5] = __float2bfloat16_rn(b.y);
+      tmp[6] = __float2bfloat16_rn(b.z); tmp[7] = __float2bfloat16_rn(b.w);
+    } else {
+      tmp[0] = __float2half_rn(a.x); tmp[1] = __float2half_rn(a.y);
+      tmp[2] = __float2half_rn(a.z); tmp[3] = __float2half_rn(a.w);
+      tmp[4] = __float2half_rn(b.x); tmp[5] = __float2half_rn(b.y);
+      tmp[6] = __float2half_rn(b.z); tmp[7] = __float2half_rn(b.w);
+    }
+    *reinterpret_cast<uint4*>(dst + i * 8) = *reinterpret_cast<const uint4*>(tmp);
+  }
+  // tail (n not a multiple of 8)
+  if (blockIdx.x == 0) {
+    for (size_t i = n8 * 8 + threadIdx.x; i < n; i += blockDim.x) {
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) dst[i] = __float2bfloat16_rn(src[i]);
+      else dst[i] = __float2half_rn(src[i]);
+    }
+  }
+}
+
+}  // namespace rfa
+
+extern "C" int rfa_version(void) { return 100; }
+extern "C" int rfa_seq_tile(void) { return 128; }
+
+extern "C" int rfa_bwd_prepare(const void* out, const void* dout, const float* lse, float* delta, float* lse2,
+                               float* dq_acc, int B, int Sq, int Hq, int D, int dtype, int* status, void* stream) {
+  using namespace rfa;
+  (void)status;
+  if (!out || !dout || !lse || !delta || !lse2) return RFA_ERR_INVALID_ARG;
+  if (B <= 0 || Sq <= 0 || Hq <= 0) return RFA_ERR_INVALID_ARG;
+  if (padded_head_dim(D) == 0) return RFA_ERR_UNSUPPORTED;
+  if (dtype != RFA_DTYPE_BF16 && dtype != RFA_DTYPE_FP16) return RFA_ERR_UNSUPPORTED;
+  const int Spad = round_up(Sq, 128);
+  const long long rows = static_cast<long long>(B) * Spad * Hq;
+  const int threads = 256;
+  long long blocks = (rows + 7) / 8;  // 8 warps per block, one row per warp per pass
+  if (blocks > 148ll * 32) blocks = 148ll * 32;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == RFA_DTYPE_BF16)
+    bwd_prepare_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), threads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(dout), lse, delta, lse2, dq_acc, B,
+        Sq, Spad, Hq, D);
+  else
+    bwd_prepare_kernel<__half><<<static_cast<unsigned>(blocks), threads, 0, s>>>(
+        static_cast<const __half*>(out), static_cast<const __half*>(dout), lse, delta, lse2, dq_acc, B, Sq, Spad, Hq,
+        D);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" int rfa_cast_from_f32(const float* src, void* dst, size_t n, int dtype, void* stream) {
+  using namespace rfa;
+  if (!src || !dst) return RFA_ERR_INVALID_ARG;
+  if (dtype != RFA_DTYPE_BF16 && dtype != RFA_DTYPE_FP16) return RFA_ERR_UNSUPPORTED;
+  if (n == 0) return RFA_OK;
+  if ((reinterpret_cast<uintptr_t>(src) & 15u) || (reinterpret_cast<uintptr_t>(dst) & 15u)) return RFA_ERR_INVALID_ARG;
+  const size_t n8 = n / 8;
+  size_t blocks = (n8 + 255) / 256;
+  if (blocks > 148u * 16) blocks = 148u * 16;
+  if (blocks == 0) blocks = 1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == RFA_DTYPE_BF16)
+    cast_from_f32_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        src, static_cast<__nv_bfloat16*>(dst), n8, n);
+  else
+    cast_from_f32_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, s>>>(src, static_cast<__half*>(dst), n8, n);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" int rfa_pack_kv(const void* k, const void* v, void* dst, size_t bytes_each, void* stream) {
+  if (!k || !v || !dst) return RFA_ERR_INVALID_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(dst, k, bytes_each, cudaMemcpyDeviceToDevice, s);
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(static_cast<char*>(dst) + bytes_each, v, bytes_each, cudaMemcpyDeviceToDevice, s);
+  if (e != cudaSuccess) cudaGetLastError();
+  return rfa::cuda_status(e);
+}

@@ -1,0 +1,557 @@
+// Backward ring hop against one K/V block.  One CTA owns a 128-row K/V tile of
+// one kv head and walks over every query head of its GQA group and every query
+// tile that can see it.  Five tensor-core products per (kv tile, q tile) pair,
+// all computed in the transposed orientation so that the kv row is the TMEM
+// lane and the accumulators dK, dV stay resident in tensor memory:
+//   S^T  = K Q^T                (smem x smem)      -> P^T = exp2(scale*S^T - lse2[q])
+//   dP^T = V dO^T               (smem x smem)      -> dS^T = P^T o (dP^T - delta[q])
+//   dV  += P^T dO               (P^T from tensor memory, dO MN-major)
+//   dK  += dS^T Q               (dS^T from shared memory, Q MN-major)
+//   dQ^T = K^T dS^T             (both MN-major), reduced into the fp32 dQ
+//                                accumulator in global memory with red.add.f32
+// The epilogue adds the partial dK/dV that arrived from the previous rank and
+// writes the packed fp32 buffer that travels on.  This one kernel covers the
+// reference's `_bwd_dq_kernel` (optimized_ring_flash_attn.py:672-735),
+// `_bwd_dkdv_kernel` (optimized_ring_flash_attn.py:738-805) and the accumulate
+// kernels (optimized_ring_flash_attn.py:441-503); S and dP are computed once
+// instead of once per kernel.
+//
+// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 4-7 elementwise
+// (P^T, dS^T, dV epilogue), warps 8-11 dQ reduction and dK epilogue.
+// Tensor memory: [0,BQ) S^T / P^T, [BQ,2BQ) dP^T then dQ^T, then dV (DH) and dK (DH).
+// Head dim 256 runs as two CTAs per tile, each owning 128 columns of dK, dV, dQ.
+#include "common.h"
+#include "tc05.cuh"
+
+namespace rfa {
+
+struct BwdParams {
+  const float* lse2;
+  const float* delta;
+  float* dq_acc;
+  const float* dkdv_prev;
+  float* dkdv_out;
+  int B, Sq, Skv, Hq, Hkv, D;
+  int Spad;
+  float scale, scale_log2;
+  int accumulate_prev, causal;
+  int* status;
+};
+
+template <int DP, int DH, int BQ, int NST>
+struct BwdCfg {
+  static constexpr int kPanels = DP / 64;
+  static constexpr int kHalves = DP / DH;
+  static constexpr int kKBytes = 128 * DP * 2;
+  static constexpr int kQBytes = BQ * DP * 2;
+  static constexpr int kDSBytes = 128 * BQ * 2;
+  static constexpr int kStatBytes = 2 * BQ * 4;
+  static constexpr int kOffK = 0;
+  static constexpr int kOffV = kKBytes;
+  static constexpr int kOffQ = 2 * kKBytes;
+  static constexpr int kOffDO = kOffQ + NST * kQBytes;
+  static constexpr int kOffDS = kOffDO + NST * kQBytes;
+  static constexpr int kOffStat = kOffDS + kDSBytes;
+  static constexpr int kSmemUsed = kOffStat + NST * kStatBytes;
+  // Pad to more than half of the SM's shared memory so that two CTAs never share an SM
+  // (each CTA allocates the whole tensor memory).
+  static constexpr int kSmemBytes = kSmemUsed < 120 * 1024 ? 120 * 1024 : kSmemUsed;
+  static constexpr int kThreads = 384;
+  static constexpr int kTmS = 0;
+  static constexpr int kTmDP = BQ;
+  static constexpr int kTmDV = 2 * BQ;
+  static constexpr int kTmDK = 2 * BQ + DH;
+  static_assert(2 * BQ + 2 * DH <= 512, "tensor memory over budget");
+  static_assert(kSmemBytes <= 232448 - 1024, "shared memory over budget");
+};
+
+template <int DP, int DH, int BQ, int NST, typename T>
+__global__ void __launch_bounds__(384, 1)
+    bwd_hop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                   const BwdParams p) {
+  using Cfg = BwdCfg<DP, DH, BQ, NST>;
+  constexpr bool kBf16 = Pack2<T>::kIsBf16;
+  constexpr int kPanelK = 128 * 128;  // bytes per panel of a 128-row tile
+  constexpr int kPanelQ = BQ * 128;   // bytes per panel of a BQ-row tile
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint64_t bar_kv_full;
+  __shared__ uint64_t bar_q_full[NST], bar_q_empty[NST], bar_do_full[NST], bar_do_empty[NST];
+  __shared__ uint64_t bar_s_full, bar_p_ready, bar_dp_full, bar_ds_ready, bar_dq_full, bar_dq_drained, bar_final;
+  __shared__ uint32_t tmem_holder;
+  __shared__ int abort_flag;
+
+  if (*reinterpret_cast<volatile int*>(p.status) != 0) return;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const uint32_t smem_base = smem_u32(smem_raw);
+  const uint32_t s_k = smem_base + Cfg::kOffK;
+  const uint32_t s_v = smem_base + Cfg::kOffV;
+  const uint32_t s_q = smem_base + Cfg::kOffQ;
+  const uint32_t s_do = smem_base + Cfg::kOffDO;
+  const uint32_t s_ds = smem_base + Cfg::kOffDS;
+  const uint32_t s_stat = smem_base + Cfg::kOffStat;
+  uint8_t* const stat_ptr = smem_raw + Cfg::kOffStat;
+  uint8_t* const ds_ptr = smem_raw + Cfg::kOffDS;
+
+  // ---- tile coordinates: kv tiles with the most visible queries first ----
+  const int per_kvt = p.Hkv * p.B * Cfg::kHalves;
+  const int kvt = static_cast<int>(blockIdx.x) / per_kvt;
+  int rem = static_cast<int>(blockIdx.x) % per_kvt;
+  const int hf = rem % Cfg::kHalves;
+  rem /= Cfg::kHalves;
+  const int hkv = rem % p.Hkv;
+  const int b = rem / p.Hkv;
+  const int G = p.Hq / p.Hkv;
+  const int n0 = kvt * 128;
+  const int nQtiles = (p.Sq + BQ - 1) / BQ;
+  const int i_begin = p.causal ? (n0 / BQ) : 0;
+  const int nI = nQtiles - i_begin;
+  const int T_total = G * nI;
+
+  if (tid == 0) {
+    abort_flag = ((smem_base & 1023u) != 0) ? 1 : 0;  // operand tiles need 1024-byte alignment
+    mbar_init(&bar_kv_full, 1);
+    for (int i = 0; i < NST; ++i) {
+      mbar_init(&bar_q_full[i], 1);
+      mbar_init(&bar_q_empty[i], 1);
+      mbar_init(&bar_do_full[i], 1);
+      mbar_init(&bar_do_empty[i], 1);
+    }
+    mbar_init(&bar_s_full, 1);
+    mbar_init(&bar_p_ready, 128);
+    mbar_init(&bar_dp_full, 1);
+    mbar_init(&bar_ds_ready, 128);
+    mbar_init(&bar_dq_full, 1);
+    mbar_init(&bar_dq_drained, 128);
+    mbar_init(&bar_final, 1);
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_holder;
+  volatile int* abort_p = &abort_flag;
+  const bool run = (abort_flag == 0) && (T_total > 0);
+
+  auto q_head = [&](int t) { return hkv * G + t / nI; };
+  auto q_tile = [&](int t) { return i_begin + t % nI; };
+
+  if (warp == 0) {
+    // =========================== TMA producer ===========================
+    if (lane == 0 && run) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_do);
+      mbar_expect_tx(&bar_kv_full, 2 * Cfg::kKBytes);
+#pragma unroll
+      for (int pn = 0; pn < Cfg::kPanels; ++pn) {
+        tma_load_4d(s_k + pn * kPanelK, &tm_k, &bar_kv_full, pn * 64, hkv, n0, b);
+        tma_load_4d(s_v + pn * kPanelK, &tm_v, &bar_kv_full, pn * 64, hkv, n0, b);
+      }
+      for (int t = 0; t < T_total; ++t) {
+        const int st = t % NST;
+        const uint32_t par_empty = ((t / NST) & 1) ^ 1;
+        const int hq = q_head(t);
+        const int i = q_tile(t);
+        // dO first: its slot frees earlier (after the dV product) than the Q slot (after dK).
+        if (!mbar_wait(&bar_do_empty[st], par_empty, abort_p)) break;
+        mbar_expect_tx(&bar_do_full[st], Cfg::kQBytes);
+#pragma unroll
+        for (int pn = 0; pn < Cfg::kPanels; ++pn)
+          tma_load_4d(s_do + st * Cfg::kQBytes + pn * kPanelQ, &tm_do, &bar_do_full[st], pn * 64, hq, i * BQ, b);
+        if (!mbar_wait(&bar_q_empty[st], par_empty, abort_p)) break;
+        mbar_expect_tx(&bar_q_full[st], Cfg::kQBytes + Cfg::kStatBytes);
+#pragma unroll
+        for (int pn = 0; pn < Cfg::kPanels; ++pn)
+          tma_load_4d(s_q + st * Cfg::kQBytes + pn * kPanelQ, &tm_q, &bar_q_full[st], pn * 64, hq, i * BQ, b);
+        const size_t stat_off = (static_cast<size_t>(b) * p.Hq + hq) * p.Spad + static_cast<size_t>(i) * BQ;
+        bulk_load_1d(s_stat + st * Cfg::kStatBytes, p.lse2 + stat_off, BQ * 4, &bar_q_full[st]);
+        bulk_load_1d(s_stat + st * Cfg::kStatBytes + BQ * 4, p.delta + stat_off, BQ * 4, &bar_q_full[st]);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0 && run) {
+      constexpr uint32_t idesc_s = make_idesc(128, BQ, kBf16, false, false);   // K-major x K-major
+      constexpr uint32_t idesc_dv = make_idesc(128, DH, kBf16, false, true);   // A tmem / K-major smem, B MN-major
+      constexpr uint32_t idesc_dq = make_idesc(128, BQ, kBf16, true, true);    // both MN-major
+      const uint32_t tm_s = tmem_base + Cfg::kTmS;
+      const uint32_t tm_dp = tmem_base + Cfg::kTmDP;
+      const uint32_t tm_dv = tmem_base + Cfg::kTmDV;
+      const uint32_t tm_dk = tmem_base + Cfg::kTmDK;
+
+      // S^T[128 x BQ] = K[128 x DP] * Q[BQ x DP]^T
+      auto issue_s = [&](int st) {
+#pragma unroll
+        for (int ks = 0; ks < DP / 16; ++ks) {
+          const uint32_t a = s_k + (ks >> 2) * kPanelK + (ks & 3) * 32;
+          const uint32_t bq = s_q + st * Cfg::kQBytes + (ks >> 2) * kPanelQ + (ks & 3) * 32;
+          mma_ss(tm_s, desc_kmajor(a), desc_kmajor(bq), idesc_s, ks > 0 ? 1u : 0u);
+        }
+      };
+      // dP^T[128 x BQ] = V[128 x DP] * dO[BQ x DP]^T
+      auto issue_dp = [&](int st) {
+#pragma unroll
+        for (int ks = 0; ks < DP / 16; ++ks) {
+          const uint32_t a = s_v + (ks >> 2) * kPanelK + (ks & 3) * 32;
+          const uint32_t bo = s_do + st * Cfg::kQBytes + (ks >> 2) * kPanelQ + (ks & 3) * 32;
+          mma_ss(tm_dp, desc_kmajor(a), desc_kmajor(bo), idesc_s, ks > 0 ? 1u : 0u);
+        }
+      };
+      // dV[128 x DH] += P^T[128 x BQ] (tensor memory) * dO[BQ x DH]
+      auto issue_dv = [&](int st, bool acc) {
+#pragma unroll
+        for (int ks = 0; ks < BQ / 16; ++ks) {
+          const uint32_t bo = s_do + st * Cfg::kQBytes + hf * (DH / 64) * kPanelQ + ks * 2048;
+          mma_ts(tm_dv, tm_s + ks * 8, desc_mnmajor(bo, kPanelQ), idesc_dv, (acc || ks > 0) ? 1u : 0u);
+        }
+      };
+      // dK[128 x DH] += dS^T[128 x BQ] (shared memory, K-major) * Q[BQ x DH]
+      auto issue_dk = [&](int st, bool acc) {
+#pragma unroll
+        for (int ks = 0; ks < BQ / 16; ++ks) {
+          const uint32_t a = s_ds + (ks >> 2) * kPanelK + (ks & 3) * 32;
+          const uint32_t bq = s_q + st * Cfg::kQBytes + hf * (DH / 64) * kPanelQ + ks * 2048;
+          mma_ss(tm_dk, desc_kmajor(a), desc_mnmajor(bq, kPanelQ), idesc_dv, (acc || ks > 0) ? 1u : 0u);
+        }
+      };
+      // dQ^T[128 (d) x BQ] = K^T[d x 128 (kv)] * dS^T[128 (kv) x BQ]; for head dim 64 the upper 64
+      // rows of the A operand run into the V tile (results in those lanes are ignored).
+      auto issue_dq = [&]() {
+#pragma unroll
+        for (int ks = 0; ks < 128 / 16; ++ks) {
+          const uint32_t a = s_k + hf * (DH / 64) * kPanelK + ks * 2048;
+          const uint32_t bs = s_ds + ks * 2048;
+          mma_ss(tm_dp, desc_mnmajor(a, kPanelK), desc_mnmajor(bs, kPanelK), idesc_dq, ks > 0 ? 1u : 0u);
+        }
+      };
+
+      bool ok = mbar_wait(&bar_kv_full, 0, abort_p);
+      if (ok) ok = mbar_wait(&bar_q_full[0], 0, abort_p);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_s(0);
+        mma_commit(&bar_s_full);
+        ok = mbar_wait(&bar_do_full[0], 0, abort_p);
+      }
+      if (ok) {
+        tc_fence_after_sync();
+        issue_dp(0);
+        mma_commit(&bar_dp_full);
+      }
+      for (int t = 0; t < T_total && ok; ++t) {
+        const int st = t % NST;
+        const int st_n = (t + 1) % NST;
+        const uint32_t par_n = ((t + 1) / NST) & 1;
+        const bool more = (t + 1 < T_total);
+        if (!mbar_wait(&bar_p_ready, t & 1, abort_p)) break;
+        tc_fence_after_sync();
+        issue_dv(st, t > 0);
+        mma_commit(&bar_do_empty[st]);
+        if (NST >= 2 && more) {
+          if (!mbar_wait(&bar_q_full[st_n], par_n, abort_p)) break;
+          tc_fence_after_sync();
+          issue_s(st_n);
+          mma_commit(&bar_s_full);
+        }
+        if (!mbar_wait(&bar_ds_ready, t & 1, abort_p)) break;
+        tc_fence_after_sync();
+        issue_dk(st, t > 0);
+        mma_commit(&bar_q_empty[st]);
+        issue_dq();
+        mma_commit(&bar_dq_full);
+        if (NST == 1 && more) {
+          if (!mbar_wait(&bar_q_full[st_n], par_n, abort_p)) break;
+          tc_fence_after_sync();
+          issue_s(st_n);
+          mma_commit(&bar_s_full);
+        }
+        if (more) {
+          if (!mbar_wait(&bar_do_full[st_n], par_n, abort_p)) break;
+          if (!mbar_wait(&bar_dq_drained, t & 1, abort_p)) break;
+          tc_fence_after_sync();
+          issue_dp(st_n);
+          mma_commit(&bar_dp_full);
+        } else {
+          mma_commit(&bar_final);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 4 && warp < 8) {
+    // =========================== elementwise warpgroup ===========================
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // kv row inside the tile
+    const int kvpos = n0 + row;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t a_s = tmem_base + lane_addr + Cfg::kTmS;
+    const uint32_t a_dp = tmem_base + lane_addr + Cfg::kTmDP;
+    bool ok = run;
+    for (int t = 0; t < T_total && ok; ++t) {
+      const int st = t % NST;
+      const int i = q_tile(t);
+      const float* lse2_s = reinterpret_cast<const float*>(stat_ptr + st * Cfg::kStatBytes);
+      const float* delta_s = lse2_s + BQ;
+      if (!mbar_wait_warp(&bar_q_full[st], (t / NST) & 1, abort_p)) { ok = false; break; }
+      if (!mbar_wait_warp(&bar_s_full, t & 1, abort_p)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int q0 = i * BQ;
+      const bool masked = p.causal && (q0 < n0 + 127);
+      uint32_t pk[BQ / 2];
+#pragma unroll
+      for (int c = 0; c < BQ / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(a_s + c * 32, r);
+        tmem_ld_wait32(r);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float4 l4 = *reinterpret_cast<const float4*>(lse2_s + c * 32 + k * 4);
+          float e0 = fast_exp2(fmaf(__uint_as_float(r[4 * k + 0]), p.scale_log2, -l4.x));
+          float e1 = fast_exp2(fmaf(__uint_as_float(r[4 * k + 1]), p.scale_log2, -l4.y));
+          float e2 = fast_exp2(fmaf(__uint_as_float(r[4 * k + 2]), p.scale_log2, -l4.z));
+          float e3 = fast_exp2(fmaf(__uint_as_float(r[4 * k + 3]), p.scale_log2, -l4.w));
+          if (masked) {
+            const int qp = q0 + c * 32 + k * 4;
+            if (qp + 0 < kvpos) e0 = 0.f;
+            if (qp + 1 < kvpos) e1 = 0.f;
+            if (qp + 2 < kvpos) e2 = 0.f;
+            if (qp + 3 < kvpos) e3 = 0.f;
+          }
+          pk[c * 16 + 2 * k + 0] = Pack2<T>::pack(e0, e1);
+          pk[c * 16 + 2 * k + 1] = Pack2<T>::pack(e2, e3);
+        }
+        uint32_t u[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) u[k] = pk[c * 16 + k];
+        tmem_st16(a_s + c * 16, u);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&bar_p_ready);
+
+      if (!mbar_wait_warp(&bar_dp_full, t & 1, abort_p)) { ok = false; break; }
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < BQ / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(a_dp + c * 32, r);
+        tmem_ld_wait32(r);
+        uint32_t w[16];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float4 d4 = *reinterpret_cast<const float4*>(delta_s + c * 32 + k * 4);
+          const float2 p01 = Pack2<T>::unpack(pk[c * 16 + 2 * k + 0]);
+          const float2 p23 = Pack2<T>::unpack(pk[c * 16 + 2 * k + 1]);
+          const float s0 = p01.x * (__uint_as_float(r[4 * k + 0]) - d4.x);
+          const float s1 = p01.y * (__uint_as_float(r[4 * k + 1]) - d4.y);
+          const float s2 = p23.x * (__uint_as_float(r[4 * k + 2]) - d4.z);
+          const float s3 = p23.y * (__uint_as_float(r[4 * k + 3]) - d4.w);
+          w[2 * k + 0] = Pack2<T>::pack(s0, s1);
+          w[2 * k + 1] = Pack2<T>::pack(s2, s3);
+        }
+        // 32 columns = 64 bytes = four 16-byte chunks of panel (c*32)/64
+        uint8_t* panel = ds_ptr + ((c * 32) / 64) * kPanelK;
+        const int chunk0 = ((c * 32) % 64) / 8;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint4 v4 = make_uint4(w[4 * k + 0], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+          *reinterpret_cast<uint4*>(panel + sw128_offset(row, chunk0 + k)) = v4;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(&bar_ds_ready);
+    }
+    // ---- epilogue: dV ----
+    if (ok) ok = mbar_wait_warp(&bar_final, 0, abort_p);
+    if (ok) {
+      tc_fence_after_sync();
+      const bool row_ok = kvpos < p.Skv;
+      const size_t base = (((static_cast<size_t>(1) * p.B + b) * p.Skv + kvpos) * p.Hkv + hkv) * p.D + hf * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + lane_addr + Cfg::kTmDV + c * 32, r);
+        tmem_ld_wait32(r);
+        if (row_ok) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int d = hf * DH + c * 32 + k * 4;
+            if (d < p.D) {
+              float4 v = make_float4(__uint_as_float(r[4 * k + 0]), __uint_as_float(r[4 * k + 1]),
+                                     __uint_as_float(r[4 * k + 2]), __uint_as_float(r[4 * k + 3]));
+              if (p.accumulate_prev) {
+                const float4 o = *reinterpret_cast<const float4*>(p.dkdv_prev + base + c * 32 + k * 4);
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              }
+              *reinterpret_cast<float4*>(p.dkdv_out + base + c * 32 + k * 4) = v;
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 8) {
+    // =========================== dQ reduction warpgroup ===========================
+    const int quarter = warp & 3;
+    const int drow = quarter * 32 + lane;  // row of dQ^T = head-dim index inside this CTA's half
+    const int d = hf * DH + drow;
+    const bool d_ok = (drow < DH) && (d < p.D);
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t a_dq = tmem_base + lane_addr + Cfg::kTmDP;
+    bool ok = run;
+    for (int t = 0; t < T_total && ok; ++t) {
+      const int hq = q_head(t);
+      const int q0 = q_tile(t) * BQ;
+      if (!mbar_wait_warp(&bar_dq_full, t & 1, abort_p)) { ok = false; break; }
+      tc_fence_after_sync();
+      float* dq_base = p.dq_acc + ((static_cast<size_t>(b) * p.Sq + q0) * p.Hq + hq) * p.D + d;
+      const size_t q_stride = static_cast<size_t>(p.Hq) * p.D;
+#pragma unroll 1
+      for (int c = 0; c < BQ / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(a_dq + c * 32, r);
+        tmem_ld_wait32(r);
+        if (c == BQ / 32 - 1) {
+          // all reads of dQ^T are complete: the region may be overwritten by the next dP^T
+          tc_fence_before_sync();
+          mbar_arrive(&bar_dq_drained);
+        }
+        if (d_ok) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const int qpos = q0 + c * 32 + k;
+            if (qpos < p.Sq) atomicAdd(dq_base + (c * 32 + k) * q_stride, __uint_as_float(r[k]) * p.scale);
+          }
+        }
+      }
+    }
+    // ---- epilogue: dK ----
+    if (ok) ok = mbar_wait_warp(&bar_final, 0, abort_p);
+    if (ok) {
+      tc_fence_after_sync();
+      const int kvpos = n0 + drow;
+      const bool row_ok = kvpos < p.Skv;
+      const size_t base = (((static_cast<size_t>(0) * p.B + b) * p.Skv + kvpos) * p.Hkv + hkv) * p.D + hf * DH;
+#pragma unroll 1
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + lane_addr + Cfg::kTmDK + c * 32, r);
+        tmem_ld_wait32(r);
+        if (row_ok) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int dd = hf * DH + c * 32 + k * 4;
+            if (dd < p.D) {
+              float4 v = make_float4(__uint_as_float(r[4 * k + 0]) * p.scale, __uint_as_float(r[4 * k + 1]) * p.scale,
+                                     __uint_as_float(r[4 * k + 2]) * p.scale, __uint_as_float(r[4 * k + 3]) * p.scale);
+              if (p.accumulate_prev) {
+                const float4 o = *reinterpret_cast<const float4*>(p.dkdv_prev + base + c * 32 + k * 4);
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              }
+              *reinterpret_cast<float4*>(p.dkdv_out + base + c * 32 + k * 4) = v;
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  }
+
+  // ---- teardown ----
+  tc_fence_before_sync();
+  __syncthreads();
+  if (abort_flag) {
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    if (tid == 0) atomicExch(p.status, kStatusWaitTimeout);
+  }
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int DP, int DH, int BQ, int NST, typename T>
+static int launch_bwd(const void* q, const void* k, const void* v, const void* dout, const BwdParams& prm, int dtype,
+                      cudaStream_t stream) {
+  using Cfg = BwdCfg<DP, DH, BQ, NST>;
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = make_tmap_bshd(&tq, q, dtype, prm.B, prm.Sq, prm.Hq, prm.D, BQ)) != RFA_OK) return rc;
+  if ((rc = make_tmap_bshd(&tdo, dout, dtype, prm.B, prm.Sq, prm.Hq, prm.D, BQ)) != RFA_OK) return rc;
+  if ((rc = make_tmap_bshd(&tk, k, dtype, prm.B, prm.Skv, prm.Hkv, prm.D, 128)) != RFA_OK) return rc;
+  if ((rc = make_tmap_bshd(&tv, v, dtype, prm.B, prm.Skv, prm.Hkv, prm.D, 128)) != RFA_OK) return rc;
+  auto kern = bwd_hop_kernel<DP, DH, BQ, NST, T>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
+    attr_done = true;
+  }
+  const unsigned grid = static_cast<unsigned>(ceil_div(prm.Skv, 128)) * prm.Hkv * prm.B * Cfg::kHalves;
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, tdo, prm);
+  return cuda_status(cudaGetLastError());
+}
+
+template <typename T>
+static int dispatch_bwd(int dp, const void* q, const void* k, const void* v, const void* dout, const BwdParams& prm,
+                        int dtype, cudaStream_t stream) {
+  switch (dp) {
+    case 64: return launch_bwd<64, 64, 128, 2, T>(q, k, v, dout, prm, dtype, stream);
+    case 128: return launch_bwd<128, 128, 128, 2, T>(q, k, v, dout, prm, dtype, stream);
+    case 256: return launch_bwd<256, 128, 64, 1, T>(q, k, v, dout, prm, dtype, stream);
+    default: return RFA_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace rfa
+
+extern "C" int rfa_bwd_hop(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
+                           const float* delta, float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B, int Sq,
+                           int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale, int accumulate_prev,
+                           int causal_diag, int* status, void* stream) {
+  using namespace rfa;
+  if (!q || !k || !v || !dout || !lse2 || !delta || !dq_acc || !dkdv_out || !status) return RFA_ERR_INVALID_ARG;
+  if (accumulate_prev && !dkdv_prev) return RFA_ERR_INVALID_ARG;
+  if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0) return RFA_ERR_INVALID_ARG;
+  if (!(softmax_scale > 0.f)) return RFA_ERR_INVALID_ARG;
+  if (causal_diag && Sq != Skv) return RFA_ERR_INVALID_ARG;
+  const int dp = padded_head_dim(D);
+  if (dp == 0) return RFA_ERR_UNSUPPORTED;
+  if (dtype != RFA_DTYPE_BF16 && dtype != RFA_DTYPE_FP16) return RFA_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(lse2) & 15u) || (reinterpret_cast<uintptr_t>(delta) & 15u) ||
+      (reinterpret_cast<uintptr_t>(dkdv_out) & 15u) || (reinterpret_cast<uintptr_t>(dkdv_prev) & 15u))
+    return RFA_ERR_INVALID_ARG;
+  BwdParams prm;
+  prm.lse2 = lse2;
+  prm.delta = delta;
+  prm.dq_acc = dq_acc;
+  prm.dkdv_prev = dkdv_prev;
+  prm.dkdv_out = dkdv_out;
+  prm.B = B;
+  prm.Sq = Sq;
+  prm.Skv = Skv;
+  prm.Hq = Hq;
+  prm.Hkv = Hkv;
+  prm.D = D;
+  prm.Spad = round_up(Sq, 128);
+  prm.scale = softmax_scale;
+  prm.scale_log2 = softmax_scale * 1.4426950408889634f;
+  prm.accumulate_prev = accumulate_prev ? 1 : 0;
+  prm.causal = causal_diag ? 1 : 0;
+  prm.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == RFA_DTYPE_BF16) return dispatch_bwd<__nv_bfloat16>(dp, q, k, v, dout, prm, dtype, s);
+  return dispatch_bwd<__half>(dp, q, k, v, dout, prm, dtype, s);
+}

@@ -1,0 +1,125 @@
+"""Host-side ring schedules: which hop kernel runs on which K/V block, and when buffers move.
+
+Forward follows ``_ring_forward_native`` (optimized_ring_flash_attn.py:818-867):
+rank r holds K/V block ``(r - step) mod W`` at step ``step``; with ``causal`` a
+rank computes only while ``step <= rank``, the elementwise mask applies only to
+its own block (step 0), and its result is final at ``step == rank``.
+
+Backward follows ``_ring_backward_native`` (optimized_ring_flash_attn.py:946-1029):
+a second ring carries the fp32 partial dK/dV of the block a rank currently
+holds; slot algebra ``prev_slot = (step - 1) & 1``, the W-th send returns the
+sums to the block's owner (``final_slot = (W - 1) & 1``).
+
+Differences from the reference, on purpose: a world size of 1 runs with no
+communication at all; the fp32 running state replaces the per-hop merge kernel;
+dQ, dK and dV of a hop come from one fused kernel.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _native, workspace
+from .transport import RingTransport
+
+
+_transports = {}
+
+
+def _transport(group, device: torch.device, tag: str) -> RingTransport:
+    """One transport (and side stream) per (group, device, ring) for the life of the process."""
+    key = (id(group) if group is not None else None, str(device), tag)
+    t = _transports.get(key)
+    if t is None or t.world_size != dist.get_world_size(group):
+        t = RingTransport(group, device)
+        _transports[key] = t
+    return t
+
+
+def _world(group) -> Tuple[int, int]:
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_world_size(group), dist.get_rank(group)
+    return 1, 0
+
+
+def ring_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float, causal: bool,
+                 kernels=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns ``(out [B,S,Hq,D] in q's dtype, lse_padded [B,Hq,Spad] fp32)``; both are fresh tensors."""
+    kn = kernels if kernels is not None else _native
+    W, rank = _world(group)
+    B, S, Hq, D = q.shape
+    ws = workspace.forward_workspace(q, k, W)
+    out = torch.empty_like(q)
+    lse = torch.empty(B, Hq, _native.padded_seq(S), dtype=torch.float32, device=q.device)
+
+    if W == 1:
+        kn.fwd_hop(q, k, v, None, None, None, out, lse, softmax_scale, True, True, causal, ws.status)
+        return out, lse
+
+    comm = _transport(group, q.device, "fwd_kv")
+    kn.pack_kv(k, v, ws.kv_send)
+    cur = ws.kv_send
+    k_cur, v_cur = k, v
+    last_step = rank if causal else W - 1
+    for step in range(W):
+        if step + 1 < W:
+            comm.post(cur, ws.kv_recv[step & 1])
+        if (not causal) or step <= rank:
+            kn.fwd_hop(q, k_cur, v_cur, ws.acc, ws.m, ws.l, out, lse, softmax_scale,
+                       step == 0, step == last_step, causal and step == 0, ws.status)
+        if step + 1 < W:
+            comm.wait()
+            cur = ws.kv_recv[step & 1]
+            k_cur, v_cur = cur[0], cur[1]
+    return out, lse
+
+
+def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                  lse: torch.Tensor, softmax_scale: float, causal: bool, kernels=None):
+    """Returns ``(dq, dk, dv)`` in the input dtypes."""
+    kn = kernels if kernels is not None else _native
+    W, rank = _world(group)
+    ws = workspace.backward_workspace(q, k, W)
+    dout = dout.contiguous()
+    kn.bwd_prepare(out, dout, lse, ws.delta, ws.lse2, ws.dq_acc, ws.status)
+
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+
+    if W == 1:
+        buf = ws.dkdv[0]
+        kn.bwd_hop(q, k, v, dout, ws.lse2, ws.delta, ws.dq_acc, None, buf, softmax_scale, False, causal, ws.status)
+        kn.cast_from_f32(ws.dq_acc, dq)
+        kn.cast_from_f32(buf[0], dk)
+        kn.cast_from_f32(buf[1], dv)
+        return dq, dk, dv
+
+    kv_comm = _transport(group, q.device, "bwd_kv")
+    dkv_comm = _transport(group, q.device, "bwd_dkdv")
+    kn.pack_kv(k, v, ws.kv_send)
+    cur = ws.kv_send
+    k_cur, v_cur = k, v
+    for step in range(W):
+        if step + 1 < W:
+            kv_comm.post(cur, ws.kv_recv[step & 1])
+        prev_slot = (step - 1) & 1
+        buf = ws.dkdv[prev_slot]
+        if step > 0:
+            dkv_comm.wait()  # partial dK/dV of the block now held has arrived in dkdv[prev_slot]
+        if (not causal) or step <= rank:
+            kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, buf if step > 0 else None, buf,
+                       softmax_scale, step > 0, causal and step == 0, ws.status)
+        if step + 1 < W:
+            kv_comm.wait()
+            cur = ws.kv_recv[step & 1]
+            k_cur, v_cur = cur[0], cur[1]
+        dkv_comm.post(buf, ws.dkdv[step & 1])
+    dkv_comm.wait()
+    final = ws.dkdv[(W - 1) & 1]
+    kn.cast_from_f32(ws.dq_acc, dq)
+    kn.cast_from_f32(final[0], dk)
+    kn.cast_from_f32(final[1], dv)
+    return dq, dk, dv

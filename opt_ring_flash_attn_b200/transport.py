@@ -1,0 +1,84 @@
+"""Ring transport: one packed buffer to the next rank, one from the previous rank, per hop.
+
+Mirrors ``DoubleBufRingComm`` of the reference (optimized_ring_flash_attn.py:163-188):
+``post(send, recv)`` issues one isend + one irecv as a single batch and returns
+immediately; ``wait()`` completes the oldest outstanding batch.  Ranks are
+group-local ring positions mapped to global ranks for sub-groups
+(optimized_ring_flash_attn.py:168-172).
+
+On CUDA the batch runs on the process group's NCCL stream: NCCL orders it after
+everything already enqueued on the stream it was posted from, and ``wait()``
+makes that stream wait for the transfer without blocking the host, so the
+transfer of hop s+1's block overlaps the kernels of hop s.  With ``side_stream``
+the post/wait pair is issued from a dedicated stream and fenced to the compute
+stream with events, which keeps the compute stream free of transport waits
+until the data is actually needed.
+"""
+from __future__ import annotations
+
+from collections import deque
+from typing import Deque, List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+class RingTransport:
+    def __init__(self, group: Optional[dist.ProcessGroup], device: torch.device, side_stream: bool = True):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+        nxt = (self.rank + 1) % self.world_size
+        prv = (self.rank - 1) % self.world_size
+        if group is not None:
+            nxt = dist.get_global_rank(group, nxt)
+            prv = dist.get_global_rank(group, prv)
+        self.send_rank = nxt
+        self.recv_rank = prv
+        self.device = device
+        self._cuda = device.type == "cuda"
+        self._stream = torch.cuda.Stream(device=device) if (self._cuda and side_stream) else None
+        # FIFO of (requests, completion event or None)
+        self._pending: Deque[List] = deque()
+        self.posted = 0  # number of batches posted (for tests and the bench's byte accounting)
+        self.bytes_sent = 0
+
+    def post(self, send_buf: torch.Tensor, recv_buf: torch.Tensor) -> None:
+        """Ship ``send_buf`` to the next rank and receive ``recv_buf`` from the previous one (async)."""
+        if send_buf.data_ptr() == recv_buf.data_ptr():
+            raise RuntimeError("ring transport: send and receive buffers must differ")
+        ops = [
+            dist.P2POp(dist.isend, send_buf, self.send_rank, group=self.group),
+            dist.P2POp(dist.irecv, recv_buf, self.recv_rank, group=self.group),
+        ]
+        self.posted += 1
+        self.bytes_sent += send_buf.numel() * send_buf.element_size()
+        if self._stream is None:
+            self._pending.append([dist.batch_isend_irecv(ops), None])
+            return
+        compute = torch.cuda.current_stream(self.device)
+        ready = torch.cuda.Event()
+        ready.record(compute)  # everything that produced send_buf / last read recv_buf
+        self._stream.wait_event(ready)
+        with torch.cuda.stream(self._stream):
+            reqs = dist.batch_isend_irecv(ops)
+            for r in reqs:
+                r.wait()  # side stream waits for the NCCL stream; the host does not block
+            done = torch.cuda.Event()
+            done.record(self._stream)
+        self._pending.append([reqs, done])
+
+    def wait(self) -> None:
+        """Make the current stream (or the host, on CPU) wait for the oldest outstanding batch."""
+        if not self._pending:
+            raise RuntimeError("ring transport: wait() without a posted transfer")
+        reqs, done = self._pending.popleft()
+        if done is None:
+            for r in reqs:
+                r.wait()
+        else:
+            torch.cuda.current_stream(self.device).wait_event(done)
+
+    def drain(self) -> None:
+        while self._pending:
+            self.wait()

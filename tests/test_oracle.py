@@ -1,0 +1,67 @@
+"""The oracle against the reference's own outputs (golden fixtures) and against dense attention."""
+import numpy as np
+import pytest
+import torch
+
+from oracle.ring_attn_oracle import dense_attention, make_inputs, ring_attn_oracle, shard
+
+CASES = [
+    "ref_test_shape_dense", "ref_test_shape_causal", "small_w4_dense", "small_w4_causal",
+    "gqa_w2_causal", "scaled_w2_causal", "config1_w8_causal",
+]
+
+
+def _cat(parts, dim=1):
+    return torch.cat(list(parts), dim=dim)
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_oracle_matches_reference_fixture(golden, name):
+    seed, B, S, Hq, Hkv, D, W, causal, stride = [int(x) for x in golden[f"{name}/meta"]]
+    scale = float(golden[f"{name}/scale"][0])
+    scale = None if scale < 0 else scale
+    q, k, v, dout = make_inputs(seed, B, S, Hq, Hkv, D)
+    # the fixture's inputs came from the same generator: guard against RNG drift
+    chk = golden[f"{name}/input_checksum"]
+    got = np.array([x.double().sum().item() for x in (q, k, v, dout)])
+    np.testing.assert_allclose(got, chk, rtol=0, atol=1e-6)
+
+    res = ring_attn_oracle(shard(q, W), shard(k, W), shard(v, W), shard(dout, W), causal=bool(causal),
+                           softmax_scale=scale)
+    # tolerance: the reference's own tests use atol 1e-3 (ring_attn.py:868, 890-892); the restatement
+    # follows the same operation order, so it is held to 2e-5 absolute here.
+    for key in ("out", "dq", "dk", "dv"):
+        mine = _cat(res[key])[:, ::stride].numpy()
+        np.testing.assert_allclose(mine, golden[f"{name}/{key}"], rtol=0, atol=2e-5, err_msg=f"{name}/{key}")
+    lse = _cat(res["lse"], dim=2)[:, :, ::stride].numpy()
+    np.testing.assert_allclose(lse, golden[f"{name}/lse"], rtol=0, atol=2e-5, err_msg=f"{name}/lse")
+
+
+@pytest.mark.parametrize("W,causal,Hq,Hkv", [(1, True, 2, 1), (1, False, 2, 2), (3, True, 4, 2), (4, False, 2, 1)])
+def test_oracle_matches_dense_attention(W, causal, Hq, Hkv):
+    B, S_total, D = 2, 96 * W, 16
+    q, k, v, dout = make_inputs(3, B, S_total, Hq, Hkv, D)
+    q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    out_d, lse_d = dense_attention(q, k, v, causal, softmax_scale=0.2)
+    out_d.backward(dout)
+    res = ring_attn_oracle(shard(q.detach(), W), shard(k.detach(), W), shard(v.detach(), W), shard(dout, W),
+                           causal=causal, softmax_scale=0.2, head_chunk=2)
+    assert torch.allclose(_cat(res["out"]), out_d.detach(), atol=1e-5)
+    assert torch.allclose(_cat(res["lse"], 2), lse_d.detach(), atol=1e-5)
+    assert torch.allclose(_cat(res["dq"]), q.grad, atol=2e-5)
+    assert torch.allclose(_cat(res["dk"]), k.grad, atol=2e-5)
+    assert torch.allclose(_cat(res["dv"]), v.grad, atol=2e-5)
+
+
+def test_merge_identity():
+    """Online-softmax merge identity of the reference's merge kernel (optimized_ring_flash_attn.py:377-383):
+    merging two blocks by their LSEs equals attention over their union."""
+    q, k, v, _ = make_inputs(9, 1, 64, 2, 2, 16)
+    o_all, lse_all = dense_attention(q, k, v, False)
+    o1, l1 = dense_attention(q, k[:, :32], v[:, :32], False)
+    o2, l2 = dense_attention(q, k[:, 32:], v[:, 32:], False)
+    lse = torch.logaddexp(l1, l2)
+    w1 = torch.exp(l1 - lse).transpose(1, 2).unsqueeze(-1)
+    w2 = torch.exp(l2 - lse).transpose(1, 2).unsqueeze(-1)
+    assert torch.allclose(o1 * w1 + o2 * w2, o_all, atol=1e-6)
+    assert torch.allclose(lse, lse_all, atol=1e-6)
