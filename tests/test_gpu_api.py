@@ -1,0 +1,77 @@
+"""The public operator on one GPU (no process group): autograd, repeated calls, argument checks."""
+import pytest
+import torch
+
+from oracle.ring_attn_oracle import make_inputs, ring_attn_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel_l2(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm()).item()
+
+
+def test_autograd_single_gpu():
+    from opt_ring_flash_attn_b200 import ring_flash_attn, ring_flash_attn_with_lse
+
+    dev = torch.device("cuda:0")
+    q, k, v, dout = (x.to(dev) for x in make_inputs(21, 2, 384, 4, 2, 128, dtype=torch.bfloat16))
+    q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    out = ring_flash_attn(q, k, v, causal=True)
+    out.backward(dout)
+    ref = ring_attn_oracle([q.detach()], [k.detach()], [v.detach()], [dout], causal=True)
+    assert (out.float() - ref["out"][0]).abs().max().item() <= 1e-2
+    assert _rel_l2(q.grad, ref["dq"][0]) <= 2e-2
+    assert _rel_l2(k.grad, ref["dk"][0]) <= 2e-2
+    assert _rel_l2(v.grad, ref["dv"][0]) <= 2e-2
+    _, lse = ring_flash_attn_with_lse(q.detach(), k.detach(), v.detach(), causal=True)
+    assert (lse - ref["lse"][0]).abs().max().item() <= 1e-3
+
+
+def test_two_calls_do_not_alias_saved_tensors():
+    """Two same-shape calls (two layers) before either backward: the first call's saved out/lse must survive."""
+    from opt_ring_flash_attn_b200 import ring_flash_attn
+
+    dev = torch.device("cuda:0")
+    a = [x.to(dev) for x in make_inputs(30, 1, 256, 2, 2, 64, dtype=torch.bfloat16)]
+    b = [x.to(dev) for x in make_inputs(31, 1, 256, 2, 2, 64, dtype=torch.bfloat16)]
+    for t in a[:3] + b[:3]:
+        t.requires_grad_(True)
+    out_a = ring_flash_attn(a[0], a[1], a[2], causal=True)
+    out_b = ring_flash_attn(b[0], b[1], b[2], causal=True)
+    (out_a.float() * a[3].float()).sum().backward()
+    (out_b.float() * b[3].float()).sum().backward()
+    for inp in (a, b):
+        ref = ring_attn_oracle([inp[0].detach()], [inp[1].detach()], [inp[2].detach()], [inp[3]], causal=True)
+        assert _rel_l2(inp[0].grad, ref["dq"][0]) <= 2e-2
+        assert _rel_l2(inp[1].grad, ref["dk"][0]) <= 2e-2
+        assert _rel_l2(inp[2].grad, ref["dv"][0]) <= 2e-2
+
+
+def test_argument_errors():
+    from opt_ring_flash_attn_b200 import ring_flash_attn
+
+    dev = torch.device("cuda:0")
+    q = torch.zeros(1, 128, 4, 64, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(NotImplementedError):
+        ring_flash_attn(q, q, q, causal=True, zigzag=True)
+    with pytest.raises(AssertionError):
+        ring_flash_attn(q, q, q, causal=False, zigzag=True)
+    with pytest.raises(AssertionError):
+        ring_flash_attn(q, q[:, :, :3], q[:, :, :3])
+    with pytest.raises(ValueError):
+        ring_flash_attn(q.float(), q.float(), q.float())
+    with pytest.raises(ValueError):
+        ring_flash_attn(q[..., :60], q[..., :60], q[..., :60])
+
+
+def test_non_contiguous_inputs():
+    from opt_ring_flash_attn_b200 import ring_flash_attn
+
+    dev = torch.device("cuda:0")
+    q, k, v, _ = (x.to(dev) for x in make_inputs(33, 1, 128, 2, 2, 64, dtype=torch.bfloat16))
+    qt = q.transpose(1, 2).contiguous().transpose(1, 2)  # same values, permuted strides
+    assert not qt.is_contiguous()
+    o1 = ring_flash_attn(q, k, v)
+    o2 = ring_flash_attn(qt, k, v)
+    assert torch.equal(o1, o2)
