@@ -1,0 +1,417 @@
+#!/usr/bin/env python
+"""Benchmark of the ring-flash-attention hot path: causal forward + backward per step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c2|c3|c4|c5] [--impl reference]
+
+N > 1 is launched with ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N``.
+One JSON line is printed by rank 0.
+
+Workload (``config.workload``): BASELINE config 3 by default -- bf16 causal GQA attention shaped like
+Llama-3-8B, B=1, S_local=8192 per rank, H_q=32, H_kv=8, D=128, q/k/v ~ N(0,1), dout ~ N(0,1) -- the
+configuration the 60%-of-peak target is quoted on.  Synthetic seeded inputs (the reference's harness
+also uses torch.randn).
+
+FLOP accounting (algorithmic, causal FLOPs counted, not executed tiles):
+  F_blk = 4*B*H_q*S_local^2*D per full block forward; the diagonal block counts 1/2; backward = 2.5x,
+  forward+backward = 3.5x.  Rank r executes (r + 1/2) block-equivalents; the slowest rank is W-1.
+  ``value`` is the whole-job rate (sum over ranks, W^2/2 block-equivalents) / slowest-rank time;
+  ``slowest_rank_tflops_per_gpu`` is the per-GPU figure of the slowest rank, 3.5*(W-1/2)*F_blk / t.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CONFIGS = {
+    # name: (B, S_local, Hq, Hkv, D, softmax_scale, std, seed, description)
+    "c2": (1, 1024, 32, 32, 128, None, 1.0, 1, "short-shard MHA B=1 S_local=1024 H=32 D=128"),
+    "c3": (1, 8192, 32, 8, 128, None, 1.0, 2, "Llama-3-8B-shaped GQA B=1 S_local=8192 Hq=32 Hkv=8 D=128"),
+    "c4": (2, 4096, 16, 16, 256, 1.0 / 16, 1.0, 3, "large head_dim MHA B=2 S_local=4096 H=16 D=256"),
+    "c5": (1, 131072, 64, 8, 128, None, 0.5, 4, "long-context GQA B=1 S_local=131072 Hq=64 Hkv=8 D=128"),
+}
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return d, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def f_blk(B, S, Hq, D):
+    return 4.0 * B * Hq * float(S) * float(S) * D
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(self.index),
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_shard(cfg, rank: int, device, dtype=torch.bfloat16, pinned=False):
+    """Per-rank shards drawn from a per-rank seeded generator (seed*1009 + rank): q, k, v, dout."""
+    B, S, Hq, Hkv, D, _, std, seed, _ = cfg
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed * 1009 + rank)
+
+    def draw(h, s):
+        t = torch.empty(B, S, h, D, dtype=dtype, pin_memory=pinned)
+        # drawn in fp32 blocks to bound host memory, then cast
+        for b in range(B):
+            for s0 in range(0, S, 4096):
+                s1 = min(S, s0 + 4096)
+                t[b, s0:s1] = (torch.randn(s1 - s0, h, D, generator=g) * s).to(dtype)
+        return t
+
+    q, k, v = draw(Hq, std), draw(Hkv, std), draw(Hkv, std)
+    dout = draw(Hq, 1.0)
+    if device is not None:
+        return [x.to(device) for x in (q, k, v, dout)]
+    return [q, k, v, dout]
+
+
+def run_reference_arm(args, cfg, name):
+    """CPU arm: the oracle port of the reference's ring_attn.py on the host cores, bounded sample."""
+    from oracle.ring_attn_oracle import ring_attn_oracle
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    B, S, Hq, Hkv, D, scale, std, seed, desc = cfg
+    # bounded sample: one GQA group pair, a quarter of the rows (at most 2048), world size 1, causal
+    G = Hq // Hkv
+    hs_kv = min(Hkv, 2)
+    hs_q = hs_kv * G
+    Ss = min(S, 2048)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, Ss, hs_q, D, generator=g) * std
+    k = torch.randn(B, Ss, hs_kv, D, generator=g) * std
+    v = torch.randn(B, Ss, hs_kv, D, generator=g) * std
+    do = torch.randn(B, Ss, hs_q, D, generator=g)
+    flops = 3.5 * 0.5 * f_blk(B, Ss, hs_q, D)
+
+    def step():
+        ring_attn_oracle([q], [k], [v], [do], causal=True, softmax_scale=scale, head_chunk=G)
+
+    for _ in range(max(1, min(args.warmup, 1))):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    val = flops / dt / 1e12
+    sample = f"{desc}: sample B={B} S_local={Ss} Hq={hs_q} Hkv={hs_kv} D={D}, world size 1, fp32, causal fwd+bwd"
+    line = {
+        "impl": "reference", "metric": "causal_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name + ": " + desc, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline_leg(cfg, budget_s=20.0):
+    """Oracle port timed on the host cores on a bounded sample of the workload (rank 0, N=1 only)."""
+    from oracle.ring_attn_oracle import ring_attn_oracle
+
+    B, S, Hq, Hkv, D, scale, std, seed, desc = cfg
+    G = Hq // Hkv
+    hs_kv = 1
+    hs_q = G
+    Ss = min(S, 2048)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, Ss, hs_q, D, generator=g) * std
+    k = torch.randn(B, Ss, hs_kv, D, generator=g) * std
+    v = torch.randn(B, Ss, hs_kv, D, generator=g) * std
+    do = torch.randn(B, Ss, hs_q, D, generator=g)
+    flops = 3.5 * 0.5 * f_blk(B, Ss, hs_q, D)
+    ring_attn_oracle([q], [k], [v], [do], causal=True, softmax_scale=scale, head_chunk=G)  # warm-up
+    n, t0 = 0, time.perf_counter()
+    while True:
+        ring_attn_oracle([q], [k], [v], [do], causal=True, softmax_scale=scale, head_chunk=G)
+        n += 1
+        if time.perf_counter() - t0 > budget_s / 2 or n >= 20:
+            break
+    dt = (time.perf_counter() - t0) / n
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"B={B} S_local={Ss} Hq={hs_q} Hkv={hs_kv} D={D}, world size 1, fp32 oracle, causal fwd+bwd, "
+                      f"{n} runs of {dt * 1e3:.0f} ms"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    B, S, Hq, Hkv, D, scale, std, seed, desc = cfg
+
+    if args.impl == "reference":
+        run_reference_arm(args, cfg, args.config)
+        return
+
+    import torch.distributed as dist
+
+    from opt_ring_flash_attn_b200 import _native, ring_flash_attn
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _native.load()
+    warmup = max(args.warmup, 3)
+    peaks, peak_kind = load_peaks()
+
+    q, k, v, dout = make_shard(cfg, rank, dev)
+    qg, kg, vg = (x.clone().requires_grad_(True) for x in (q, k, v))
+
+    def step_device():
+        qg.grad = kg.grad = vg.grad = None
+        out = ring_flash_attn(qg, kg, vg, softmax_scale=scale, causal=True)
+        out.backward(dout)
+        return out
+
+    flush = None
+    bytes_resident = sum(x.numel() * x.element_size() for x in (q, k, v, dout)) * 2 + q.numel() * 4
+    if bytes_resident < 2 * 126 * 2 ** 20:
+        flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        step_device()
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _native.launch_count()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for i in range(args.steps):
+        if flush is not None:
+            flush.fill_(i & 0xFF)
+        ev[i][0].record()
+        step_device()
+        ev[i][1].record()
+    barrier()
+    launches = _native.launch_count() - launches0
+    ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- dominant kernel alone: backward hop on this rank's own (diagonal) block ----
+    from opt_ring_flash_attn_b200 import workspace
+
+    out_d, lse_d = None, None
+    with torch.no_grad():
+        from opt_ring_flash_attn_b200 import schedule
+
+        # single-device forward of the diagonal block gives out/lse for the backward kernel
+        spad = _native.padded_seq(S)
+        out_d = torch.empty_like(q)
+        lse_d = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
+        st = torch.zeros(1, dtype=torch.int32, device=dev)
+        sc = D ** -0.5 if scale is None else scale
+        _native.fwd_hop(q, k, v, None, None, None, out_d, lse_d, sc, True, True, True, st)
+        delta = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
+        lse2 = torch.empty_like(delta)
+        dq_acc = torch.empty(_native.dq_acc_elems(B, S, Hq, D), dtype=torch.float32, device=dev)
+        dkdv = torch.empty(2, B, S, Hkv, D, dtype=torch.float32, device=dev)
+        _native.bwd_prepare(out_d, dout, lse_d, delta, lse2, dq_acc, st)
+        kreps = max(3, min(args.steps, 10))
+        for _ in range(2):
+            _native.bwd_hop(q, k, v, dout, lse2, delta, dq_acc, None, dkdv, sc, False, True, st)
+        torch.cuda.synchronize()
+        k_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(kreps)]
+        for i in range(kreps):
+            if flush is not None:
+                flush.fill_(i & 0xFF)
+            k_ev[i][0].record()
+            _native.bwd_hop(q, k, v, dout, lse2, delta, dq_acc, None, dkdv, sc, False, True, st)
+            k_ev[i][1].record()
+        torch.cuda.synchronize()
+        bwd_ms = sum(a.elapsed_time(b) for a, b in k_ev) / kreps
+        f_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(kreps)]
+        for i in range(kreps):
+            if flush is not None:
+                flush.fill_(i & 0xFF)
+            f_ev[i][0].record()
+            _native.fwd_hop(q, k, v, None, None, None, out_d, lse_d, sc, True, True, True, st)
+            f_ev[i][1].record()
+        torch.cuda.synchronize()
+        fwd_ms = sum(a.elapsed_time(b) for a, b in f_ev) / kreps
+        _native.check_status(st, "bench kernels")
+
+    # ---- end to end through the public API with host buffers ----
+    e2e = None
+    if not args.no_e2e:
+        hq, hk, hv, hdo = make_shard(cfg, rank, None, pinned=True)
+        h_out = torch.empty_like(hq).pin_memory()
+        h_dq = torch.empty_like(hq).pin_memory()
+        h_dk = torch.empty_like(hk).pin_memory()
+        h_dv = torch.empty_like(hv).pin_memory()
+        dq_, dk_, dv_, ddo_ = (torch.empty_like(x, device=dev) for x in (hq, hk, hv, hdo))
+
+        def step_e2e():
+            dq_.copy_(hq, non_blocking=True)
+            dk_.copy_(hk, non_blocking=True)
+            dv_.copy_(hv, non_blocking=True)
+            ddo_.copy_(hdo, non_blocking=True)
+            a, b_, c = (x.detach().requires_grad_(True) for x in (dq_, dk_, dv_))
+            o = ring_flash_attn(a, b_, c, softmax_scale=scale, causal=True)
+            o.backward(ddo_)
+            h_out.copy_(o.detach(), non_blocking=True)
+            h_dq.copy_(a.grad, non_blocking=True)
+            h_dk.copy_(b_.grad, non_blocking=True)
+            h_dv.copy_(c.grad, non_blocking=True)
+
+        for _ in range(2):
+            step_e2e()
+        barrier()
+        e_steps = max(3, min(args.steps, 10))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e_steps):
+            step_e2e()
+        e1.record()
+        barrier()
+        te = torch.tensor([e0.elapsed_time(e1) / e_steps], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_ms = float(te.item())
+        h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv, hdo))
+        d2h = sum(x.numel() * x.element_size() for x in (h_out, h_dq, h_dk, h_dv))
+    status_ok = True
+    for ws in list(workspace._fwd_cache.values()) + list(workspace._bwd_cache.values()):
+        _native.check_status(ws.status, "bench")
+
+    if rank == 0:
+        W = world
+        fb = f_blk(B, S, Hq, D)
+        flops_job = 3.5 * (W * W / 2.0) * fb
+        flops_slowest = 3.5 * (W - 0.5) * fb
+        value = flops_job / (ms_max * 1e-3) / 1e12
+        slowest = flops_slowest / (ms_max * 1e-3) / 1e12
+        peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+        peak_sus = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+        bwd_flops = 2.5 * 0.5 * fb
+        fwd_flops = 0.5 * fb
+        achieved = bwd_flops / (bwd_ms * 1e-3) / 1e12
+        line = {
+            "metric": "causal_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": W, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.config}: {desc}, causal, fwd+bwd, world size {W}",
+                       "l2": "L2 flushed (256 MiB write) between timed steps" if flush is not None
+                             else "per-step inputs+outputs exceed the 126 MB L2",
+                       "flops": "algorithmic causal FLOPs: 3.5*(W^2/2)*4*B*Hq*S_local^2*D for the job"},
+            "slowest_rank_tflops_per_gpu": slowest,
+            "slowest_rank_frac_of_peak": slowest / peak_sus,
+            "peak_used_for_step": {"bf16_tflops_sustained": peak_sus, "kind": peak_kind},
+            "roofline": {"bound": "tensor", "kernel": "bwd_hop_kernel (diagonal block)", "achieved": achieved,
+                         "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_kind": peak_kind + " burst",
+                         "traffic": None, "ms_per_launch": bwd_ms,
+                         "fwd_hop": {"achieved": fwd_flops / (fwd_ms * 1e-3) / 1e12, "ms_per_launch": fwd_ms,
+                                     "frac": fwd_flops / (fwd_ms * 1e-3) / 1e12 / peak}},
+            "gpu_launches": launches, "clocks": clocks,
+        }
+        if e2e is None and not args.no_e2e:
+            line["e2e"] = {"value": flops_job / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        if W == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_leg(cfg)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

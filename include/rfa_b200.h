@@ -75,19 +75,24 @@ int rfa_fwd_hop(const void* q, const void* k, const void* v, float* acc, float* 
                 int B, int Sq, int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale, int first, int last,
                 int causal_diag, int* status, void* stream);
 
+/* Number of fp32 elements of the dQ accumulator (private tiled layout that makes the
+ * per-tile reductions of the backward hop 16-byte vector operations; opaque to the caller). */
+size_t rfa_dq_acc_elems(int B, int Sq, int Hq, int D);
+
 /*
  * Backward preprocessing, once per backward pass:
  *   delta[b,h,s] = sum_d out[b,s,h,d] * dout[b,s,h,d]
  *   lse2[b,h,s]  = lse[b,h,s] * log2(e)      (rows s >= Sq: lse2 = +inf, delta = 0)
- * and, when dq_acc != NULL, dq_acc[B,Sq,Hq,D] (fp32) is cleared.
- * Replaces `_bwd_preprocess_kernel` (optimized_ring_flash_attn.py:645-669).
+ * and, when dq_acc != NULL, the dQ accumulator (rfa_dq_acc_elems floats) is cleared.
+ * Replaces `_bwd_preprocess_kernel` (optimized_ring_flash_attn.py:645-669) and the
+ * `is_first` overwrite of `_dq_accum_kernel` (optimized_ring_flash_attn.py:441-460).
  */
 int rfa_bwd_prepare(const void* out, const void* dout, const float* lse, float* delta, float* lse2, float* dq_acc,
                     int B, int Sq, int Hq, int D, int dtype, int* status, void* stream);
 
 /*
  * One ring hop of the backward pass against one K/V block:
- *   dq_acc[B,Sq,Hq,D] (fp32)  +=  scale * dS  K
+ *   dq_acc (fp32, rfa_dq_acc_elems)  +=  scale * dS  K
  *   dkdv_out[0] = (accumulate_prev ? dkdv_prev[0] : 0) + scale * dS^T Q
  *   dkdv_out[1] = (accumulate_prev ? dkdv_prev[1] : 0) + P^T dO
  * with P = exp2(scale*log2e * Q K^T - lse2), dS = P o (dO V^T - delta).
@@ -103,8 +108,14 @@ int rfa_bwd_hop(const void* q, const void* k, const void* v, const void* dout, c
                 void* stream);
 
 /*
+ * dq[B,Sq,Hq,D] = (dtype) dq_acc: converts the accumulated dQ out of its private layout.
+ * Replaces `dq_acc.to(q.dtype)` (optimized_ring_flash_attn.py:1027).
+ */
+int rfa_bwd_dq_finalize(const float* dq_acc, void* dq, int B, int Sq, int Hq, int D, int dtype, void* stream);
+
+/*
  * dst[i] = (dtype) src[i] for n elements.  Replaces the final `.to(q.dtype)`
- * casts of the fp32 gradient accumulators (optimized_ring_flash_attn.py:1027-1029).
+ * casts of the fp32 dK/dV buffers (optimized_ring_flash_attn.py:1028-1029).
  */
 int rfa_cast_from_f32(const float* src, void* dst, size_t n, int dtype, void* stream);
 
@@ -124,6 +135,14 @@ int rfa_pack_kv(const void* k, const void* v, void* dst, size_t bytes_each, void
  * No counterpart in the reference.
  */
 int rfa_debug_mma_probe(int mode, const void* a, const void* b, float* c, int* status, void* stream);
+
+/*
+ * Diagnostic: when `buf` is non-NULL, the hop kernels launched afterwards record per-role pipeline
+ * events of their first `n_ctas` CTAs into buf, laid out [n_ctas][5 roles][cap] 64-bit words
+ * (tag << 48 | SM clock; roles: 0 loader, 1 MMA issuer, 2/3 elementwise groups, 4 dQ reduction).
+ * NULL switches tracing off.  Host-side state; not thread safe.  No counterpart in the reference.
+ */
+int rfa_debug_set_trace(unsigned long long* buf, int n_ctas, int cap);
 
 #ifdef __cplusplus
 }

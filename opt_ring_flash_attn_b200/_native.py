@@ -33,12 +33,15 @@ SIGNATURES = {
     "rfa_version": (_i, []),
     "rfa_seq_tile": (_i, []),
     "rfa_fwd_acc_elems": (_sz, [_i, _i, _i, _i]),
+    "rfa_dq_acc_elems": (_sz, [_i, _i, _i, _i]),
+    "rfa_bwd_dq_finalize": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "rfa_fwd_hop": (_i, [_vp] * 8 + [_i] * 7 + [_f] + [_i] * 3 + [_vp, _vp]),
     "rfa_bwd_prepare": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp]),
     "rfa_bwd_hop": (_i, [_vp] * 9 + [_i] * 7 + [_f] + [_i] * 2 + [_vp, _vp]),
     "rfa_cast_from_f32": (_i, [_vp, _vp, _sz, _i, _vp]),
     "rfa_pack_kv": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "rfa_debug_mma_probe": (_i, [_i, _vp, _vp, _vp, _vp, _vp]),
+    "rfa_debug_set_trace": (_i, [_vp, _i, _i]),
 }
 
 
@@ -65,9 +68,19 @@ def load() -> ctypes.CDLL:
     return lib
 
 
-def _check(rc: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of kernels of this library launched so far by this process (memcpy-only calls excluded)."""
+    return _launches
+
+
+def _check(rc: int, what: str, kernels: int = 1) -> None:
+    global _launches
     if rc != RFA_OK:
         raise RuntimeError(f"{what} failed: {ERROR_NAMES.get(rc, rc)}")
+    _launches += kernels
 
 
 def _stream(stream: Optional[torch.cuda.Stream]) -> int:
@@ -123,6 +136,19 @@ def bwd_hop(q, k, v, dout, lse2, delta, dq_acc, dkdv_prev, dkdv_out, softmax_sca
     _check(rc, "rfa_bwd_hop")
 
 
+def dq_acc_elems(B: int, Sq: int, Hq: int, D: int) -> int:
+    n = load().rfa_dq_acc_elems(B, Sq, Hq, D)
+    if n == 0:
+        raise RuntimeError(f"unsupported shape for the dQ accumulator: B={B} S={Sq} H={Hq} D={D}")
+    return n
+
+
+def dq_finalize(dq_acc: torch.Tensor, dq: torch.Tensor, stream=None) -> None:
+    B, Sq, Hq, D = dq.shape
+    rc = load().rfa_bwd_dq_finalize(_ptr(dq_acc), _ptr(dq), B, Sq, Hq, D, DTYPE_CODES[dq.dtype], _stream(stream))
+    _check(rc, "rfa_bwd_dq_finalize")
+
+
 def cast_from_f32(src: torch.Tensor, dst: torch.Tensor, stream=None) -> None:
     assert src.dtype == torch.float32 and src.numel() == dst.numel()
     rc = load().rfa_cast_from_f32(_ptr(src), _ptr(dst), src.numel(), DTYPE_CODES[dst.dtype], _stream(stream))
@@ -132,12 +158,19 @@ def cast_from_f32(src: torch.Tensor, dst: torch.Tensor, stream=None) -> None:
 def pack_kv(k: torch.Tensor, v: torch.Tensor, dst: torch.Tensor, stream=None) -> None:
     nbytes = k.numel() * k.element_size()
     rc = load().rfa_pack_kv(_ptr(k), _ptr(v), _ptr(dst), nbytes, _stream(stream))
-    _check(rc, "rfa_pack_kv")
+    _check(rc, "rfa_pack_kv", kernels=0)
 
 
 def mma_probe(mode: int, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, status: torch.Tensor, stream=None) -> None:
     rc = load().rfa_debug_mma_probe(mode, _ptr(a), _ptr(b), _ptr(c), _ptr(status), _stream(stream))
     _check(rc, "rfa_debug_mma_probe")
+
+
+def set_trace(buf: Optional[torch.Tensor], n_ctas: int = 0, cap: int = 0) -> None:
+    """Diagnostics: record pipeline events of the first ``n_ctas`` CTAs of later hop launches into ``buf``
+    (int64/uint64 tensor of n_ctas*5*cap elements); ``None`` switches tracing off."""
+    rc = load().rfa_debug_set_trace(_ptr(buf), n_ctas, cap)
+    _check(rc, "rfa_debug_set_trace", kernels=0)
 
 
 def check_status(status: torch.Tensor, what: str = "ring_flash_attn") -> None:

@@ -10,6 +10,8 @@
 
 namespace rfa {
 
+TraceCfg g_trace = {nullptr, 0, 0};
+
 // cuTensorMapEncodeTiled is reached through the runtime's driver entry point
 // lookup so that the library carries no link-time dependency on libcuda.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -85,8 +87,15 @@ __device__ __forceinline__ float dot8<__half>(const uint4& a, const uint4& b) {
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_prepare_kernel(const T* __restrict__ out, const T* __restrict__ dout,
                                                          const float* __restrict__ lse, float* __restrict__ delta,
-                                                         float* __restrict__ lse2, float* __restrict__ dq_acc, int B,
-                                                         int Sq, int Spad, int Hq, int D) {
+                                                         float* __restrict__ lse2, float* __restrict__ dq_acc,
+                                                         size_t dq_vec4, int B, int Sq, int Spad, int Hq, int D) {
+  // clear the fp32 dQ accumulator (private tiled layout, dq_vec4 float4 elements)
+  if (dq_acc != nullptr) {
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < dq_vec4; i += stride)
+      reinterpret_cast<float4*>(dq_acc)[i] = z;
+  }
   const int lane = threadIdx.x & 31;
   const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -113,15 +122,53 @@ __global__ void __launch_bounds__(256) bwd_prepare_kernel(const T* __restrict__ 
       const uint4 g = *reinterpret_cast<const uint4*>(dout + row_off + v * 8);
       acc += dot8<T>(a, g);
     }
-    if (dq_acc != nullptr) {
-      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int v = lane; v < D / 4; v += 32) *reinterpret_cast<float4*>(dq_acc + row_off + v * 4) = z;
-    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (lane == 0) {
       delta[stat] = acc;
       lse2[stat] = lse[stat] * 1.4426950408889634f;
+    }
+  }
+}
+
+// dQ accumulator (fp32, tiled [b][h][tile of 128 rows][32 row groups][DP][4]) -> dq [B, Sq, Hq, D] in T.
+// One block per (b, h, tile, 64-wide slice of the head dim); transposed through shared memory so that
+// both the reads (16 B per thread, consecutive) and the writes (16 B per thread, row-contiguous) coalesce.
+template <typename T>
+__global__ void __launch_bounds__(256) dq_finalize_kernel(const float* __restrict__ acc, T* __restrict__ dq, int B,
+                                                         int Sq, int Hq, int D, int DP, int nQt) {
+  __shared__ __align__(16) T tile[128][64 + 8];
+  const int nslice = DP / 64;
+  int idx = blockIdx.x;
+  const int slice = idx % nslice; idx /= nslice;
+  const int qt = idx % nQt; idx /= nQt;
+  const int h = idx % Hq;
+  const int b = idx / Hq;
+  const float* src = acc + ((static_cast<size_t>(b) * Hq + h) * nQt + qt) * (static_cast<size_t>(128) * DP);
+  const int dl = threadIdx.x & 63;
+  const int qsub = threadIdx.x >> 6;
+#pragma unroll 2
+  for (int qg = qsub; qg < 32; qg += 4) {
+    const float4 v = *reinterpret_cast<const float4*>(src + (static_cast<size_t>(qg) * DP + slice * 64 + dl) * 4);
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      tile[4 * qg + 0][dl] = __float2bfloat16_rn(v.x); tile[4 * qg + 1][dl] = __float2bfloat16_rn(v.y);
+      tile[4 * qg + 2][dl] = __float2bfloat16_rn(v.z); tile[4 * qg + 3][dl] = __float2bfloat16_rn(v.w);
+    } else {
+      tile[4 * qg + 0][dl] = __float2half_rn(v.x); tile[4 * qg + 1][dl] = __float2half_rn(v.y);
+      tile[4 * qg + 2][dl] = __float2half_rn(v.z); tile[4 * qg + 3][dl] = __float2half_rn(v.w);
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int id = it * 256 + threadIdx.x;
+    const int q = id >> 3;
+    const int part = id & 7;
+    const int qg_ = qt * 128 + q;
+    const int d = slice * 64 + part * 8;
+    if (qg_ < Sq && d < D) {
+      const uint4 w = *reinterpret_cast<const uint4*>(&tile[q][part * 8]);
+      *reinterpret_cast<uint4*>(dq + ((static_cast<size_t>(b) * Sq + qg_) * Hq + h) * D + d) = w;
     }
   }
 }
@@ -159,6 +206,14 @@ __global__ void __launch_bounds__(256) cast_from_f32_kernel(const float* __restr
 }  // namespace rfa
 
 extern "C" int rfa_version(void) { return 100; }
+
+extern "C" int rfa_debug_set_trace(unsigned long long* buf, int n_ctas, int cap) {
+  if (buf != nullptr && (n_ctas <= 0 || cap <= 0)) return RFA_ERR_INVALID_ARG;
+  rfa::g_trace.buf = buf;
+  rfa::g_trace.ctas = buf ? n_ctas : 0;
+  rfa::g_trace.cap = buf ? cap : 0;
+  return RFA_OK;
+}
 extern "C" int rfa_seq_tile(void) { return 128; }
 
 extern "C" int rfa_bwd_prepare(const void* out, const void* dout, const float* lse, float* delta, float* lse2,
@@ -171,18 +226,44 @@ extern "C" int rfa_bwd_prepare(const void* out, const void* dout, const float* l
   if (dtype != RFA_DTYPE_BF16 && dtype != RFA_DTYPE_FP16) return RFA_ERR_UNSUPPORTED;
   const int Spad = round_up(Sq, 128);
   const long long rows = static_cast<long long>(B) * Spad * Hq;
+  const size_t dq_vec4 = static_cast<size_t>(B) * Hq * Spad * padded_head_dim(D) / 4;
+  if (dq_acc && (reinterpret_cast<uintptr_t>(dq_acc) & 15u)) return RFA_ERR_INVALID_ARG;
   const int threads = 256;
   long long blocks = (rows + 7) / 8;  // 8 warps per block, one row per warp per pass
   if (blocks > 148ll * 32) blocks = 148ll * 32;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == RFA_DTYPE_BF16)
     bwd_prepare_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), threads, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(dout), lse, delta, lse2, dq_acc, B,
-        Sq, Spad, Hq, D);
+        static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(dout), lse, delta, lse2, dq_acc,
+        dq_vec4, B, Sq, Spad, Hq, D);
   else
     bwd_prepare_kernel<__half><<<static_cast<unsigned>(blocks), threads, 0, s>>>(
-        static_cast<const __half*>(out), static_cast<const __half*>(dout), lse, delta, lse2, dq_acc, B, Sq, Spad, Hq,
-        D);
+        static_cast<const __half*>(out), static_cast<const __half*>(dout), lse, delta, lse2, dq_acc, dq_vec4, B, Sq,
+        Spad, Hq, D);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" size_t rfa_dq_acc_elems(int B, int Sq, int Hq, int D) {
+  const int dp = rfa::padded_head_dim(D);
+  if (dp == 0 || B <= 0 || Sq <= 0 || Hq <= 0) return 0;
+  return static_cast<size_t>(B) * Hq * rfa::round_up(Sq, 128) * dp;
+}
+
+extern "C" int rfa_bwd_dq_finalize(const float* dq_acc, void* dq, int B, int Sq, int Hq, int D, int dtype,
+                                   void* stream) {
+  using namespace rfa;
+  if (!dq_acc || !dq || B <= 0 || Sq <= 0 || Hq <= 0) return RFA_ERR_INVALID_ARG;
+  const int dp = padded_head_dim(D);
+  if (dp == 0) return RFA_ERR_UNSUPPORTED;
+  if (dtype != RFA_DTYPE_BF16 && dtype != RFA_DTYPE_FP16) return RFA_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(dq_acc) & 15u) || (reinterpret_cast<uintptr_t>(dq) & 15u)) return RFA_ERR_INVALID_ARG;
+  const int nQt = round_up(Sq, 128) / 128;
+  const unsigned grid = static_cast<unsigned>(B) * Hq * nQt * (dp / 64);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == RFA_DTYPE_BF16)
+    dq_finalize_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), B, Sq, Hq, D, dp, nQt);
+  else
+    dq_finalize_kernel<__half><<<grid, 256, 0, s>>>(dq_acc, static_cast<__half*>(dq), B, Sq, Hq, D, dp, nQt);
   return cuda_status(cudaGetLastError());
 }
 

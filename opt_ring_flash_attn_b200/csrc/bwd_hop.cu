@@ -16,10 +16,13 @@
 // kernels (optimized_ring_flash_attn.py:441-503); S and dP are computed once
 // instead of once per kernel.
 //
-// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 4-7 elementwise
-// (P^T, dS^T, dV epilogue), warps 8-11 dQ reduction and dK epilogue.
+// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 4-11 two elementwise
+// warpgroups (each owns half of the query columns of every tile: P^T, dS^T, then
+// the dV / dK epilogues), warps 12-15 dQ reduction.
 // Tensor memory: [0,BQ) S^T / P^T, [BQ,2BQ) dP^T then dQ^T, then dV (DH) and dK (DH).
 // Head dim 256 runs as two CTAs per tile, each owning 128 columns of dK, dV, dQ.
+#include <type_traits>
+
 #include "common.h"
 #include "tc05.cuh"
 
@@ -36,6 +39,8 @@ struct BwdParams {
   float scale, scale_log2;
   int accumulate_prev, causal;
   int* status;
+  unsigned long long* trace;
+  int trace_ctas, trace_cap;
 };
 
 template <int DP, int DH, int BQ, int NST>
@@ -56,7 +61,7 @@ struct BwdCfg {
   // Pad to more than half of the SM's shared memory so that two CTAs never share an SM
   // (each CTA allocates the whole tensor memory).
   static constexpr int kSmemBytes = kSmemUsed < 120 * 1024 ? 120 * 1024 : kSmemUsed;
-  static constexpr int kThreads = 384;
+  static constexpr int kThreads = 512;
   static constexpr int kTmS = 0;
   static constexpr int kTmDP = BQ;
   static constexpr int kTmDV = 2 * BQ;
@@ -66,7 +71,7 @@ struct BwdCfg {
 };
 
 template <int DP, int DH, int BQ, int NST, typename T>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(512, 1)
     bwd_hop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                    const BwdParams p) {
@@ -122,9 +127,9 @@ __global__ void __launch_bounds__(384, 1)
       mbar_init(&bar_do_empty[i], 1);
     }
     mbar_init(&bar_s_full, 1);
-    mbar_init(&bar_p_ready, 128);
+    mbar_init(&bar_p_ready, 256);
     mbar_init(&bar_dp_full, 1);
-    mbar_init(&bar_ds_ready, 128);
+    mbar_init(&bar_ds_ready, 256);
     mbar_init(&bar_dq_full, 1);
     mbar_init(&bar_dq_drained, 128);
     mbar_init(&bar_final, 1);
@@ -141,6 +146,12 @@ __global__ void __launch_bounds__(384, 1)
   volatile int* abort_p = &abort_flag;
   const bool run = (abort_flag == 0) && (T_total > 0);
 
+  Tracer tr;
+  {
+    int role = -1;
+    if (lane == 0) role = (warp == 0) ? 0 : (warp == 1) ? 1 : (warp == 4) ? 2 : (warp == 8) ? 3 : (warp == 12) ? 4 : -1;
+    if (role >= 0) tr.init(p.trace, p.trace_ctas, p.trace_cap, kTraceRoles, role);
+  }
   auto q_head = [&](int t) { return hkv * G + t / nI; };
   auto q_tile = [&](int t) { return i_begin + t % nI; };
 
@@ -164,11 +175,13 @@ __global__ void __launch_bounds__(384, 1)
         const int i = q_tile(t);
         // dO first: its slot frees earlier (after the dV product) than the Q slot (after dK).
         if (!mbar_wait(&bar_do_empty[st], par_empty, abort_p)) break;
+        tr.mark(40);
         mbar_expect_tx(&bar_do_full[st], Cfg::kQBytes);
 #pragma unroll
         for (int pn = 0; pn < Cfg::kPanels; ++pn)
           tma_load_4d(s_do + st * Cfg::kQBytes + pn * kPanelQ, &tm_do, &bar_do_full[st], pn * 64, hq, i * BQ, b);
         if (!mbar_wait(&bar_q_empty[st], par_empty, abort_p)) break;
+        tr.mark(41);
         mbar_expect_tx(&bar_q_full[st], Cfg::kQBytes + Cfg::kStatBytes);
 #pragma unroll
         for (int pn = 0; pn < Cfg::kPanels; ++pn)
@@ -213,7 +226,10 @@ __global__ void __launch_bounds__(384, 1)
 #pragma unroll
         for (int ks = 0; ks < BQ / 16; ++ks) {
           const uint32_t bo = s_do + st * Cfg::kQBytes + hf * (DH / 64) * kPanelQ + ks * 2048;
-          mma_ts(tm_dv, tm_s + ks * 8, desc_mnmajor(bo, kPanelQ), idesc_dv, (acc || ks > 0) ? 1u : 0u);
+          // P^T of query columns [16ks, 16ks+16): each elementwise group packs its half over its own S^T columns
+          const int grp = (ks * 16) / (BQ / 2);
+          const uint32_t pa = tm_s + grp * (BQ / 2) + ((ks * 16) % (BQ / 2)) / 2;
+          mma_ts(tm_dv, pa, desc_mnmajor(bo, kPanelQ), idesc_dv, (acc || ks > 0) ? 1u : 0u);
         }
       };
       // dK[128 x DH] += dS^T[128 x BQ] (shared memory, K-major) * Q[BQ x DH]
@@ -254,22 +270,28 @@ __global__ void __launch_bounds__(384, 1)
         const int st_n = (t + 1) % NST;
         const uint32_t par_n = ((t + 1) / NST) & 1;
         const bool more = (t + 1 < T_total);
+        tr.mark(10);
         if (!mbar_wait(&bar_p_ready, t & 1, abort_p)) break;
+        tr.mark(11);
         tc_fence_after_sync();
         issue_dv(st, t > 0);
         mma_commit(&bar_do_empty[st]);
         if (NST >= 2 && more) {
           if (!mbar_wait(&bar_q_full[st_n], par_n, abort_p)) break;
+          tr.mark(12);
           tc_fence_after_sync();
           issue_s(st_n);
           mma_commit(&bar_s_full);
         }
+        tr.mark(13);
         if (!mbar_wait(&bar_ds_ready, t & 1, abort_p)) break;
+        tr.mark(14);
         tc_fence_after_sync();
+        issue_dq();  // first: the dQ reduction and the next dP^T wait on it
+        mma_commit(&bar_dq_full);
         issue_dk(st, t > 0);
         mma_commit(&bar_q_empty[st]);
-        issue_dq();
-        mma_commit(&bar_dq_full);
+        tr.mark(15);
         if (NST == 1 && more) {
           if (!mbar_wait(&bar_q_full[st_n], par_n, abort_p)) break;
           tc_fence_after_sync();
@@ -278,118 +300,160 @@ __global__ void __launch_bounds__(384, 1)
         }
         if (more) {
           if (!mbar_wait(&bar_do_full[st_n], par_n, abort_p)) break;
+          tr.mark(16);
           if (!mbar_wait(&bar_dq_drained, t & 1, abort_p)) break;
+          tr.mark(17);
           tc_fence_after_sync();
           issue_dp(st_n);
           mma_commit(&bar_dp_full);
+          tr.mark(18);
         } else {
           mma_commit(&bar_final);
         }
       }
     }
     __syncwarp();
-  } else if (warp >= 4 && warp < 8) {
-    // =========================== elementwise warpgroup ===========================
+  } else if (warp >= 4 && warp < 12) {
+    // =========================== elementwise warpgroups ===========================
+    // Two warpgroups share every tile: group cw owns query columns [cw*BQ/2, (cw+1)*BQ/2).
+    constexpr int kHalfCols = BQ / 2;
+    constexpr int NCH = kHalfCols / 32;  // 32-column chunks per thread
+    const int cw = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // kv row inside the tile
     const int kvpos = n0 + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t a_s = tmem_base + lane_addr + Cfg::kTmS;
-    const uint32_t a_dp = tmem_base + lane_addr + Cfg::kTmDP;
+    const int col0 = cw * kHalfCols;
+    const uint32_t a_s = tmem_base + lane_addr + Cfg::kTmS + col0;
+    const uint32_t a_dp = tmem_base + lane_addr + Cfg::kTmDP + col0;
     bool ok = run;
     for (int t = 0; t < T_total && ok; ++t) {
       const int st = t % NST;
       const int i = q_tile(t);
-      const float* lse2_s = reinterpret_cast<const float*>(stat_ptr + st * Cfg::kStatBytes);
+      const float* lse2_s = reinterpret_cast<const float*>(stat_ptr + st * Cfg::kStatBytes) + col0;
       const float* delta_s = lse2_s + BQ;
       if (!mbar_wait_warp(&bar_q_full[st], (t / NST) & 1, abort_p)) { ok = false; break; }
+      tr.mark(19);
       if (!mbar_wait_warp(&bar_s_full, t & 1, abort_p)) { ok = false; break; }
+      tr.mark(20);
       tc_fence_after_sync();
-      const int q0 = i * BQ;
-      const bool masked = p.causal && (q0 < n0 + 127);
-      uint32_t pk[BQ / 2];
+      const int q0 = i * BQ + col0;
+      const bool masked = p.causal && (i * BQ < n0 + 127);
+      uint32_t pk[NCH * 16];
+      {
+        uint32_t r[NCH][32];
 #pragma unroll
-      for (int c = 0; c < BQ / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(a_s + c * 32, r);
-        tmem_ld_wait32(r);
+        for (int c = 0; c < NCH; ++c) tmem_ld32(a_s + c * 32, r[c]);
+        tmem_ld_wait32(r[0]);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float4 l4 = *reinterpret_cast<const float4*>(lse2_s + c * 32 + k * 4);
-          float e0 = fast_exp2(fmaf(__uint_as_float(r[4 * k + 0]), p.scale_log2, -l4.x));
-          float e1 = fast_exp2(fmaf(__uint_as_float(r[4 * k + 1]), p.scale_log2, -l4.y));
-          float e2 = fast_exp2(fmaf(__uint_as_float(r[4 * k + 2]), p.scale_log2, -l4.z));
-          float e3 = fast_exp2(fmaf(__uint_as_float(r[4 * k + 3]), p.scale_log2, -l4.w));
-          if (masked) {
-            const int qp = q0 + c * 32 + k * 4;
-            if (qp + 0 < kvpos) e0 = 0.f;
-            if (qp + 1 < kvpos) e1 = 0.f;
-            if (qp + 2 < kvpos) e2 = 0.f;
-            if (qp + 3 < kvpos) e3 = 0.f;
+        for (int c = 1; c < NCH; ++c) reg_fence32(r[c]);
+        tr.mark(21);
+        // P^T = exp2(scale*log2e * S^T - lse2[q]); the causal mask (query before key) only on diagonal tiles
+        auto p_phase = [&](auto mask_tag) {
+          constexpr bool kMask = decltype(mask_tag)::value;
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const float4 l4 = *reinterpret_cast<const float4*>(lse2_s + c * 32 + k * 4);
+              float e0 = fast_exp2(fmaf(__uint_as_float(r[c][4 * k + 0]), p.scale_log2, -l4.x));
+              float e1 = fast_exp2(fmaf(__uint_as_float(r[c][4 * k + 1]), p.scale_log2, -l4.y));
+              float e2 = fast_exp2(fmaf(__uint_as_float(r[c][4 * k + 2]), p.scale_log2, -l4.z));
+              float e3 = fast_exp2(fmaf(__uint_as_float(r[c][4 * k + 3]), p.scale_log2, -l4.w));
+              if (kMask) {
+                const int qp = q0 + c * 32 + k * 4;
+                if (qp + 0 < kvpos) e0 = 0.f;
+                if (qp + 1 < kvpos) e1 = 0.f;
+                if (qp + 2 < kvpos) e2 = 0.f;
+                if (qp + 3 < kvpos) e3 = 0.f;
+              }
+              pk[c * 16 + 2 * k + 0] = Pack2<T>::pack(e0, e1);
+              pk[c * 16 + 2 * k + 1] = Pack2<T>::pack(e2, e3);
+            }
           }
-          pk[c * 16 + 2 * k + 0] = Pack2<T>::pack(e0, e1);
-          pk[c * 16 + 2 * k + 1] = Pack2<T>::pack(e2, e3);
-        }
+        };
+        if (masked) p_phase(std::true_type{});
+        else p_phase(std::false_type{});
+      }
+      tr.mark(26);
+      // P^T (16 bit, two per column) goes over the start of this group's own S^T columns.
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
         uint32_t u[16];
 #pragma unroll
         for (int k = 0; k < 16; ++k) u[k] = pk[c * 16 + k];
         tmem_st16(a_s + c * 16, u);
       }
       tmem_st_wait();
+      tr.mark(27);
       tc_fence_before_sync();
       mbar_arrive(&bar_p_ready);
+      tr.mark(22);
 
       if (!mbar_wait_warp(&bar_dp_full, t & 1, abort_p)) { ok = false; break; }
+      tr.mark(23);
       tc_fence_after_sync();
+      {
+        uint32_t r[NCH][32];
 #pragma unroll
-      for (int c = 0; c < BQ / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(a_dp + c * 32, r);
-        tmem_ld_wait32(r);
-        uint32_t w[16];
+        for (int c = 0; c < NCH; ++c) tmem_ld32(a_dp + c * 32, r[c]);
+        tmem_ld_wait32(r[0]);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float4 d4 = *reinterpret_cast<const float4*>(delta_s + c * 32 + k * 4);
-          const float2 p01 = Pack2<T>::unpack(pk[c * 16 + 2 * k + 0]);
-          const float2 p23 = Pack2<T>::unpack(pk[c * 16 + 2 * k + 1]);
-          const float s0 = p01.x * (__uint_as_float(r[4 * k + 0]) - d4.x);
-          const float s1 = p01.y * (__uint_as_float(r[4 * k + 1]) - d4.y);
-          const float s2 = p23.x * (__uint_as_float(r[4 * k + 2]) - d4.z);
-          const float s3 = p23.y * (__uint_as_float(r[4 * k + 3]) - d4.w);
-          w[2 * k + 0] = Pack2<T>::pack(s0, s1);
-          w[2 * k + 1] = Pack2<T>::pack(s2, s3);
-        }
-        // 32 columns = 64 bytes = four 16-byte chunks of panel (c*32)/64
-        uint8_t* panel = ds_ptr + ((c * 32) / 64) * kPanelK;
-        const int chunk0 = ((c * 32) % 64) / 8;
+        for (int c = 1; c < NCH; ++c) reg_fence32(r[c]);
+        tr.mark(24);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          uint4 v4 = make_uint4(w[4 * k + 0], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
-          *reinterpret_cast<uint4*>(panel + sw128_offset(row, chunk0 + k)) = v4;
+        for (int c = 0; c < NCH; ++c) {
+          uint32_t w[16];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float4 d4 = *reinterpret_cast<const float4*>(delta_s + c * 32 + k * 4);
+            const float2 p01 = Pack2<T>::unpack(pk[c * 16 + 2 * k + 0]);
+            const float2 p23 = Pack2<T>::unpack(pk[c * 16 + 2 * k + 1]);
+            const float s0 = p01.x * (__uint_as_float(r[c][4 * k + 0]) - d4.x);
+            const float s1 = p01.y * (__uint_as_float(r[c][4 * k + 1]) - d4.y);
+            const float s2 = p23.x * (__uint_as_float(r[c][4 * k + 2]) - d4.z);
+            const float s3 = p23.y * (__uint_as_float(r[c][4 * k + 3]) - d4.w);
+            w[2 * k + 0] = Pack2<T>::pack(s0, s1);
+            w[2 * k + 1] = Pack2<T>::pack(s2, s3);
+          }
+          // 32 columns = 64 bytes = four 16-byte chunks inside the panel that holds column col0 + c*32
+          const int colg = col0 + c * 32;
+          uint8_t* panel = ds_ptr + (colg / 64) * kPanelK;
+          const int chunk0 = (colg % 64) / 8;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint4 v4 = make_uint4(w[4 * k + 0], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+            *reinterpret_cast<uint4*>(panel + sw128_offset(row, chunk0 + k)) = v4;
+          }
         }
       }
+      tr.mark(28);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&bar_ds_ready);
+      tr.mark(25);
     }
-    // ---- epilogue: dV ----
+    // ---- epilogue: group 0 writes dV, group 1 writes dK (scaled) ----
     if (ok) ok = mbar_wait_warp(&bar_final, 0, abort_p);
     if (ok) {
       tc_fence_after_sync();
       const bool row_ok = kvpos < p.Skv;
-      const size_t base = (((static_cast<size_t>(1) * p.B + b) * p.Skv + kvpos) * p.Hkv + hkv) * p.D + hf * DH;
+      const int which = (cw == 0) ? 1 : 0;  // packed buffer: [0] = dK, [1] = dV
+      const float mul = (cw == 0) ? 1.0f : p.scale;
+      const uint32_t a_acc = tmem_base + lane_addr + (cw == 0 ? Cfg::kTmDV : Cfg::kTmDK);
+      const size_t base = (((static_cast<size_t>(which) * p.B + b) * p.Skv + kvpos) * p.Hkv + hkv) * p.D + hf * DH;
 #pragma unroll 1
       for (int c = 0; c < DH / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + lane_addr + Cfg::kTmDV + c * 32, r);
+        tmem_ld32(a_acc + c * 32, r);
         tmem_ld_wait32(r);
         if (row_ok) {
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const int d = hf * DH + c * 32 + k * 4;
             if (d < p.D) {
-              float4 v = make_float4(__uint_as_float(r[4 * k + 0]), __uint_as_float(r[4 * k + 1]),
-                                     __uint_as_float(r[4 * k + 2]), __uint_as_float(r[4 * k + 3]));
+              float4 v = make_float4(__uint_as_float(r[4 * k + 0]) * mul, __uint_as_float(r[4 * k + 1]) * mul,
+                                     __uint_as_float(r[4 * k + 2]) * mul, __uint_as_float(r[4 * k + 3]) * mul);
               if (p.accumulate_prev) {
                 const float4 o = *reinterpret_cast<const float4*>(p.dkdv_prev + base + c * 32 + k * 4);
                 v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
@@ -401,67 +465,55 @@ __global__ void __launch_bounds__(384, 1)
       }
     }
     __syncwarp();
-  } else if (warp >= 8) {
+  } else if (warp >= 12) {
     // =========================== dQ reduction warpgroup ===========================
     const int quarter = warp & 3;
     const int drow = quarter * 32 + lane;  // row of dQ^T = head-dim index inside this CTA's half
     const int d = hf * DH + drow;
-    const bool d_ok = (drow < DH) && (d < p.D);
+    const bool d_ok = (drow < DH);
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t a_dq = tmem_base + lane_addr + Cfg::kTmDP;
+    // dQ accumulator layout (fp32, private): [b][hq][Spad/128 tiles][32 groups of 4 rows][DP][4].
+    // Lane = head-dim index, four consecutive registers = four consecutive query rows, so one
+    // 16-byte vector reduction per (lane, row group) and 512 contiguous bytes per warp instruction.
+    constexpr size_t kTileElems = static_cast<size_t>(128) * DP;
+    constexpr int NB = BQ / 64;  // batches of two 32-column chunks
+    const int nQt128 = p.Spad / 128;
     bool ok = run;
     for (int t = 0; t < T_total && ok; ++t) {
       const int hq = q_head(t);
       const int q0 = q_tile(t) * BQ;
+      tr.mark(29);
       if (!mbar_wait_warp(&bar_dq_full, t & 1, abort_p)) { ok = false; break; }
+      tr.mark(30);
       tc_fence_after_sync();
-      float* dq_base = p.dq_acc + ((static_cast<size_t>(b) * p.Sq + q0) * p.Hq + hq) * p.D + d;
-      const size_t q_stride = static_cast<size_t>(p.Hq) * p.D;
+      float* base = p.dq_acc + ((static_cast<size_t>(b) * p.Hq + hq) * nQt128 + q0 / 128) * kTileElems +
+                    (static_cast<size_t>((q0 % 128) / 4) * DP + d) * 4;
 #pragma unroll 1
-      for (int c = 0; c < BQ / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(a_dq + c * 32, r);
-        tmem_ld_wait32(r);
-        if (c == BQ / 32 - 1) {
-          // all reads of dQ^T are complete: the region may be overwritten by the next dP^T
+      for (int bt = 0; bt < NB; ++bt) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(a_dq + bt * 64, r0);
+        tmem_ld32(a_dq + bt * 64 + 32, r1);
+        tmem_ld_wait32(r0);
+        reg_fence32(r1);
+        if (bt == NB - 1) {
+          // every read of dQ^T has completed: the columns may be overwritten by the next dP^T
           tc_fence_before_sync();
           mbar_arrive(&bar_dq_drained);
+          tr.mark(31);
         }
         if (d_ok) {
+          // rows beyond Sq and head-dim columns beyond D hold exact zeros (zero-filled operands, P = 0)
 #pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            const int qpos = q0 + c * 32 + k;
-            if (qpos < p.Sq) atomicAdd(dq_base + (c * 32 + k) * q_stride, __uint_as_float(r[k]) * p.scale);
-          }
-        }
-      }
-    }
-    // ---- epilogue: dK ----
-    if (ok) ok = mbar_wait_warp(&bar_final, 0, abort_p);
-    if (ok) {
-      tc_fence_after_sync();
-      const int kvpos = n0 + drow;
-      const bool row_ok = kvpos < p.Skv;
-      const size_t base = (((static_cast<size_t>(0) * p.B + b) * p.Skv + kvpos) * p.Hkv + hkv) * p.D + hf * DH;
-#pragma unroll 1
-      for (int c = 0; c < DH / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + lane_addr + Cfg::kTmDK + c * 32, r);
-        tmem_ld_wait32(r);
-        if (row_ok) {
+          for (int k = 0; k < 8; ++k)
+            red_add_v4_f32(base + static_cast<size_t>(bt * 16 + k) * DP * 4, __uint_as_float(r0[4 * k + 0]) * p.scale,
+                           __uint_as_float(r0[4 * k + 1]) * p.scale, __uint_as_float(r0[4 * k + 2]) * p.scale,
+                           __uint_as_float(r0[4 * k + 3]) * p.scale);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int dd = hf * DH + c * 32 + k * 4;
-            if (dd < p.D) {
-              float4 v = make_float4(__uint_as_float(r[4 * k + 0]) * p.scale, __uint_as_float(r[4 * k + 1]) * p.scale,
-                                     __uint_as_float(r[4 * k + 2]) * p.scale, __uint_as_float(r[4 * k + 3]) * p.scale);
-              if (p.accumulate_prev) {
-                const float4 o = *reinterpret_cast<const float4*>(p.dkdv_prev + base + c * 32 + k * 4);
-                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-              }
-              *reinterpret_cast<float4*>(p.dkdv_out + base + c * 32 + k * 4) = v;
-            }
-          }
+          for (int k = 0; k < 8; ++k)
+            red_add_v4_f32(base + static_cast<size_t>(bt * 16 + 8 + k) * DP * 4,
+                           __uint_as_float(r1[4 * k + 0]) * p.scale, __uint_as_float(r1[4 * k + 1]) * p.scale,
+                           __uint_as_float(r1[4 * k + 2]) * p.scale, __uint_as_float(r1[4 * k + 3]) * p.scale);
         }
       }
     }
@@ -551,6 +603,9 @@ extern "C" int rfa_bwd_hop(const void* q, const void* k, const void* v, const vo
   prm.accumulate_prev = accumulate_prev ? 1 : 0;
   prm.causal = causal_diag ? 1 : 0;
   prm.status = status;
+  prm.trace = g_trace.buf;
+  prm.trace_ctas = g_trace.ctas;
+  prm.trace_cap = g_trace.cap;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == RFA_DTYPE_BF16) return dispatch_bwd<__nv_bfloat16>(dp, q, k, v, dout, prm, dtype, s);
   return dispatch_bwd<__half>(dp, q, k, v, dout, prm, dtype, s);

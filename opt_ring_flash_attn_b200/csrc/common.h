@@ -27,6 +27,15 @@ inline int padded_head_dim(int d) {
 // pads ragged sequence tails and head dimensions below the padded size.
 int make_tmap_bshd(CUtensorMap* out, const void* base, int dtype, int B, int S, int H, int D, int box_rows);
 
+// Diagnostic event trace requested through rfa_debug_set_trace (null buffer = off).
+struct TraceCfg {
+  unsigned long long* buf;
+  int ctas;
+  int cap;
+};
+extern TraceCfg g_trace;
+constexpr int kTraceRoles = 5;
+
 // Translates a CUDA runtime error into an ABI error code (and clears it).
 inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? RFA_OK : RFA_ERR_CUDA; }
 

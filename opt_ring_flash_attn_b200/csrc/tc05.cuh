@@ -250,6 +250,19 @@ __device__ __forceinline__ void tmem_ld_wait32(uint32_t (&r)[32]) {
                :
                : "memory");
 }
+// Compiler-only fence for a second register block filled by an earlier tcgen05.ld: placed after
+// tmem_ld_wait32 of the first block, it keeps uses of these registers behind the wait.
+__device__ __forceinline__ void reg_fence32(uint32_t (&r)[32]) {
+  asm volatile("" : RFA_RW8(r, 0), RFA_RW8(r, 8), RFA_RW8(r, 16), RFA_RW8(r, 24) : : "memory");
+}
+__device__ __forceinline__ void red_add_f32(float* gptr, float v) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(gptr), "f"(v) : "memory");
+}
+// 16-byte vector reduction (sm_90+): four consecutive floats, one L2 operation.
+__device__ __forceinline__ void red_add_v4_f32(float* gptr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gptr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
@@ -302,6 +315,25 @@ struct Pack2<__half> {
   __device__ __forceinline__ static float2 unpack(uint32_t u) {
     __half2 v = *reinterpret_cast<__half2*>(&u);
     return __half22float2(v);
+  }
+};
+
+// Optional per-role event trace (diagnostics): (tag << 48 | SM clock) records written by one
+// designated thread per role into a caller-provided buffer laid out [cta][role][cap].
+struct Tracer {
+  unsigned long long* buf = nullptr;
+  int cap = 0;
+  int n = 0;
+  __device__ __forceinline__ void init(unsigned long long* base, int n_ctas, int cap_, int n_roles, int role) {
+    if (base != nullptr && static_cast<int>(blockIdx.x) < n_ctas) {
+      buf = base + (static_cast<size_t>(blockIdx.x) * n_roles + role) * cap_;
+      cap = cap_;
+    }
+  }
+  __device__ __forceinline__ void mark(int tag) {
+    if (buf != nullptr && n < cap) {
+      buf[n++] = (static_cast<unsigned long long>(tag) << 48) | (static_cast<unsigned long long>(clock64()) & 0xffffffffffffull);
+    }
   }
 };
 

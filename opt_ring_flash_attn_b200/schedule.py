@@ -92,7 +92,7 @@ def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
     if W == 1:
         buf = ws.dkdv[0]
         kn.bwd_hop(q, k, v, dout, ws.lse2, ws.delta, ws.dq_acc, None, buf, softmax_scale, False, causal, ws.status)
-        kn.cast_from_f32(ws.dq_acc, dq)
+        kn.dq_finalize(ws.dq_acc, dq)
         kn.cast_from_f32(buf[0], dk)
         kn.cast_from_f32(buf[1], dv)
         return dq, dk, dv
@@ -119,7 +119,7 @@ def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
         dkv_comm.post(buf, ws.dkdv[step & 1])
     dkv_comm.wait()
     final = ws.dkdv[(W - 1) & 1]
-    kn.cast_from_f32(ws.dq_acc, dq)
+    kn.dq_finalize(ws.dq_acc, dq)
     kn.cast_from_f32(final[0], dk)
     kn.cast_from_f32(final[1], dv)
     return dq, dk, dv

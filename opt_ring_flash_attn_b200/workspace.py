@@ -38,7 +38,7 @@ class ForwardWorkspace:
 class BackwardWorkspace:
     delta: torch.Tensor               # fp32 [B, Hq, Spad]
     lse2: torch.Tensor                # fp32 [B, Hq, Spad]
-    dq_acc: torch.Tensor              # fp32 [B, S, Hq, D]
+    dq_acc: torch.Tensor              # fp32, private tiled layout (B*Hq*Spad*padded D elements)
     dkdv: List[torch.Tensor]          # 2 x fp32 [2, B, S, Hkv, D] (1 slot when world size is 1)
     kv_send: Optional[torch.Tensor]
     kv_recv: List[torch.Tensor]
@@ -88,7 +88,7 @@ def backward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int) -> Bac
     spad = _native.padded_seq(S)
     delta = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
     lse2 = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
-    dq_acc = torch.empty(B, S, Hq, D, dtype=torch.float32, device=dev)
+    dq_acc = torch.empty(B * Hq * spad * _padded_head_dim(D), dtype=torch.float32, device=dev)
     nslots = 1 if world_size == 1 else 2
     dkdv = [torch.empty(2, B, S, Hkv, D, dtype=torch.float32, device=dev) for _ in range(nslots)]
     if world_size == 1:

@@ -55,7 +55,7 @@ def emulate_backward(douts, qs, ks, vs, outs, lses_padded, scale: float, causal:
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     delta = [torch.empty(B, Hq, spad, dtype=torch.float32, device=dev) for _ in range(W)]
     lse2 = [torch.empty(B, Hq, spad, dtype=torch.float32, device=dev) for _ in range(W)]
-    dq_acc = [torch.empty(B, S, Hq, D, dtype=torch.float32, device=dev) for _ in range(W)]
+    dq_acc = [torch.empty(B * Hq * spad * _padded_head_dim(D), dtype=torch.float32, device=dev) for _ in range(W)]
     for r in range(W):
         kn.bwd_prepare(outs[r], douts[r], lses_padded[r], delta[r], lse2[r], dq_acc[r], status)
     # travelling dK/dV buffer of block kb; it starts at its owner (step 0) and moves to rank+1 each step
@@ -72,7 +72,7 @@ def emulate_backward(douts, qs, ks, vs, outs, lses_padded, scale: float, causal:
     dqs, dks, dvs = [], [], []
     for r in range(W):
         dq = torch.empty_like(qs[r]); dk = torch.empty_like(ks[r]); dv = torch.empty_like(vs[r])
-        kn.cast_from_f32(dq_acc[r], dq)
+        kn.dq_finalize(dq_acc[r], dq)
         kn.cast_from_f32(travelling[r][0], dk)
         kn.cast_from_f32(travelling[r][1], dv)
         dqs.append(dq); dks.append(dk); dvs.append(dv)
