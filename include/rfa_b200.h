@@ -40,6 +40,7 @@ extern "C" {
 #define RFA_ERR_UNSUPPORTED (-2) /* head dim not a multiple of 8 or above 256, unknown dtype */
 #define RFA_ERR_CUDA (-3)        /* a CUDA runtime call or the launch failed */
 #define RFA_ERR_DRIVER (-4)      /* the driver rejected a tensor-map descriptor */
+#define RFA_ERR_TOO_LARGE (-5)   /* the shape needs more scratch than rfa_bwd_hop_noalloc's fixed array holds */
 
 #define RFA_DTYPE_BF16 0
 #define RFA_DTYPE_FP16 1
@@ -106,6 +107,31 @@ int rfa_bwd_hop(const void* q, const void* k, const void* v, const void* dout, c
                 float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B, int Sq, int Skv, int Hq, int Hkv,
                 int D, int dtype, float softmax_scale, int accumulate_prev, int causal_diag, int* status,
                 void* stream);
+
+/*
+ * rfa_bwd_hop for callers that cannot allocate device memory (no counterpart in the reference).
+ *
+ * Same computation as rfa_bwd_hop followed by rfa_bwd_dq_finalize, but the caller passes no dQ
+ * accumulator: dq (dtype [B,Sq,Hq,D]) receives scale * dS K of THIS hop only, and the fp32
+ * accumulator the kernel needs lives in a fixed array of RFA_NOALLOC_SCRATCH_BYTES inside the library
+ * (held by every GPU that loads it, until the process exits).  Meant for hosts where cudaMalloc is
+ * off limits: a memory pool that was handed out completely at start-up, a plugin boundary that only
+ * passes tensors in and out, or a section of the program that must not enter the driver's allocator.
+ * The call itself performs no cudaMalloc/cudaFree and calls no allocating library routine.
+ *
+ *  - Shapes whose accumulator (rfa_dq_acc_elems(B,Sq,Hq,D) * 4 bytes) exceeds the array are rejected
+ *    with RFA_ERR_TOO_LARGE; nothing is launched.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current); make that first call before any stream capture begins.
+ *  - All calls on a device share the one array: it is cleared at the start of every call, and two
+ *    calls that overlap on the GPU (different streams) race on it -- issue them on one stream.
+ */
+#define RFA_NOALLOC_SCRATCH_BYTES (32u * 1024u * 1024u)
+size_t rfa_noalloc_scratch_bytes(void);
+int rfa_bwd_hop_noalloc(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
+                        const float* delta, void* dq, const float* dkdv_prev, float* dkdv_out, int B, int Sq, int Skv,
+                        int Hq, int Hkv, int D, int dtype, float softmax_scale, int accumulate_prev, int causal_diag,
+                        int* status, void* stream);
 
 /*
  * dq[B,Sq,Hq,D] = (dtype) dq_acc: converts the accumulated dQ out of its private layout.

@@ -22,6 +22,7 @@ ERROR_NAMES = {
     -2: "RFA_ERR_UNSUPPORTED",
     -3: "RFA_ERR_CUDA",
     -4: "RFA_ERR_DRIVER",
+    -5: "RFA_ERR_TOO_LARGE",
 }
 STATUS_NAMES = {0: "ok", 1: "a bounded pipeline wait inside a kernel ran out of time"}
 
@@ -38,6 +39,8 @@ SIGNATURES = {
     "rfa_fwd_hop": (_i, [_vp] * 8 + [_i] * 7 + [_f] + [_i] * 3 + [_vp, _vp]),
     "rfa_bwd_prepare": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp]),
     "rfa_bwd_hop": (_i, [_vp] * 9 + [_i] * 7 + [_f] + [_i] * 2 + [_vp, _vp]),
+    "rfa_noalloc_scratch_bytes": (_sz, []),
+    "rfa_bwd_hop_noalloc": (_i, [_vp] * 9 + [_i] * 7 + [_f] + [_i] * 2 + [_vp, _vp]),
     "rfa_cast_from_f32": (_i, [_vp, _vp, _sz, _i, _vp]),
     "rfa_pack_kv": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "rfa_debug_mma_probe": (_i, [_i, _vp, _vp, _vp, _vp, _vp]),
@@ -134,6 +137,20 @@ def bwd_hop(q, k, v, dout, lse2, delta, dq_acc, dkdv_prev, dkdv_out, softmax_sca
         _ptr(dkdv_out), B, Sq, Skv, Hq, Hkv, D, DTYPE_CODES[q.dtype], float(softmax_scale),
         int(accumulate_prev), int(causal_diag), _ptr(status), _stream(stream))
     _check(rc, "rfa_bwd_hop")
+
+
+def bwd_hop_noalloc(q, k, v, dout, lse2, delta, dq, dkdv_prev, dkdv_out, softmax_scale: float,
+                    accumulate_prev: bool, causal_diag: bool, status, stream=None) -> None:
+    """One backward hop for callers that cannot allocate: no dQ accumulator is passed, ``dq`` (q's dtype)
+    receives this hop's dQ.  The accumulator is a fixed array inside the library (see the C header for
+    the size limit, the first-call set-up and the one-stream rule)."""
+    B, Sq, Hq, D = q.shape
+    _, Skv, Hkv, _ = k.shape
+    rc = load().rfa_bwd_hop_noalloc(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(dout), _ptr(lse2), _ptr(delta), _ptr(dq), _ptr(dkdv_prev),
+        _ptr(dkdv_out), B, Sq, Skv, Hq, Hkv, D, DTYPE_CODES[q.dtype], float(softmax_scale),
+        int(accumulate_prev), int(causal_diag), _ptr(status), _stream(stream))
+    _check(rc, "rfa_bwd_hop_noalloc", kernels=2)
 
 
 def dq_acc_elems(B: int, Sq: int, Hq: int, D: int) -> int:
