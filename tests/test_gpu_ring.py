@@ -1,0 +1,87 @@
+"""The real multi-process path: one process per GPU, NCCL ring, public operator, compared with the oracle.
+Skipped when fewer than two GPUs are visible (the single-GPU emulation in test_gpu_kernels.py covers the kernels)."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, cfg, errs):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from opt_ring_flash_attn_b200 import _native, ring_flash_attn_with_lse, workspace
+        from oracle.ring_attn_oracle import make_inputs, ring_attn_oracle, shard
+
+        B, S, Hq, Hkv, D, causal, dtype = cfg
+        q, k, v, dout = (x.to(dev) for x in make_inputs(60, B, S * world, Hq, Hkv, D, dtype=dtype))
+        qs, ks, vs, dos = shard(q, world), shard(k, world), shard(v, world), shard(dout, world)
+        ql, kl, vl = (x[rank].clone().requires_grad_(True) for x in (qs, ks, vs))
+        for it in range(2):  # second iteration reuses the cached workspaces and transports
+            ql.grad = kl.grad = vl.grad = None
+            out, lse = ring_flash_attn_with_lse(ql, kl, vl, causal=causal, group=dist.group.WORLD)
+            out.backward(dos[rank])
+        torch.cuda.synchronize()
+        for ws in list(workspace._fwd_cache.values()) + list(workspace._bwd_cache.values()):
+            _native.check_status(ws.status, "ring")
+        ref = ring_attn_oracle(qs, ks, vs, dos, causal=causal, head_chunk=4)
+
+        def rel(a, b):
+            return ((a.float() - b).norm() / b.norm()).item()
+
+        assert (out.float() - ref["out"][rank]).abs().max().item() <= 1e-2
+        assert (lse - ref["lse"][rank]).abs().max().item() <= 1e-3
+        assert rel(ql.grad, ref["dq"][rank]) <= 2e-2
+        assert rel(kl.grad, ref["dk"][rank]) <= 2e-2
+        assert rel(vl.grad, ref["dv"][rank]) <= 2e-2
+        dist.barrier()
+    except Exception as e:
+        errs.put(f"rank {rank}: {type(e).__name__}: {e}")
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("cfg", [
+    (1, 512, 4, 4, 128, True, torch.bfloat16),
+    (1, 384, 8, 2, 128, False, torch.bfloat16),
+    (2, 256, 4, 2, 64, True, torch.float16),
+    (1, 320, 2, 2, 256, True, torch.bfloat16),
+])
+def test_ring_nccl(cfg):
+    import torch.multiprocessing as mp
+
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    ctx = mp.get_context("spawn")
+    errs = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, cfg, errs)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    msgs = []
+    while not errs.empty():
+        msgs.append(errs.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            msgs.append("a rank did not finish in time")
+    assert not msgs and all(p.exitcode == 0 for p in procs), msgs

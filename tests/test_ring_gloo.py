@@ -1,0 +1,108 @@
+"""Host-side ring logic on CPU ranks (gloo): schedules, slot algebra and transport, with a test double
+for the kernels.  Every rank's result is compared with the oracle on the full problem."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle.ring_attn_oracle import make_inputs, ring_attn_oracle, shard
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, causal, Hq, Hkv, use_subgroup, errs):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    try:
+        import sys
+        sys.path.insert(0, os.path.dirname(__file__))
+        import fake_kernels
+        from opt_ring_flash_attn_b200 import schedule
+
+        group = None
+        ring_world, ring_rank = world, rank
+        if use_subgroup:
+            # ranks {1, 2} form the ring; rank 0 sits out (tests group-local -> global rank mapping)
+            group = dist.new_group([1, 2])
+            if rank == 0:
+                dist.barrier()
+                return
+            ring_world, ring_rank = 2, rank - 1
+        B, S, D = 1, 96, 32
+        q, k, v, dout = make_inputs(50, B, S * ring_world, Hq, Hkv, D, dtype=torch.bfloat16)
+        qs, ks, vs, dos = shard(q, ring_world), shard(k, ring_world), shard(v, ring_world), shard(dout, ring_world)
+        scale = 0.2
+        out, lse = schedule.ring_forward(group, qs[ring_rank], ks[ring_rank], vs[ring_rank], scale, causal,
+                                         kernels=fake_kernels)
+        # a second forward before the first backward: results of call 1 must survive (no workspace aliasing)
+        out2, _ = schedule.ring_forward(group, qs[ring_rank], ks[ring_rank], vs[ring_rank], scale, causal,
+                                        kernels=fake_kernels)
+        dq, dk, dv = schedule.ring_backward(group, dos[ring_rank], qs[ring_rank], ks[ring_rank], vs[ring_rank], out,
+                                            lse, scale, causal, kernels=fake_kernels)
+        ref = ring_attn_oracle(qs, ks, vs, dos, causal=causal, softmax_scale=scale)
+        r = ring_rank
+
+        def rel(a, b):
+            return ((a.float() - b).norm() / b.norm()).item()
+
+        assert torch.equal(out, out2)
+        assert (out.float() - ref["out"][r]).abs().max().item() <= 1e-2
+        assert (lse[:, :, :S] - ref["lse"][r]).abs().max().item() <= 1e-3
+        assert rel(dq, ref["dq"][r]) <= 2e-2, rel(dq, ref["dq"][r])
+        assert rel(dk, ref["dk"][r]) <= 2e-2, rel(dk, ref["dk"][r])
+        assert rel(dv, ref["dv"][r]) <= 2e-2, rel(dv, ref["dv"][r])
+        dist.barrier()
+    except Exception as e:  # surface the failure to the parent
+        errs.put(f"rank {rank}: {type(e).__name__}: {e}")
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,causal,Hq,Hkv,sub", [(2, True, 2, 2, False), (2, False, 4, 2, False),
+                                                     (3, True, 4, 2, False), (3, True, 2, 1, True)])
+def test_ring_schedules_on_gloo(world, causal, Hq, Hkv, sub):
+    ctx = mp.get_context("spawn")
+    errs = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, causal, Hq, Hkv, sub, errs)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+    msgs = []
+    while not errs.empty():
+        msgs.append(errs.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            msgs.append("a rank did not finish in time")
+    assert not msgs and all(p.exitcode == 0 for p in procs), msgs
+
+
+def test_transport_rejects_same_buffer_and_unposted_wait():
+    """Error behaviour of the transport mirrors the reference's comm helpers (RuntimeError on misuse)."""
+    port = _free_port()
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=0, world_size=1)
+    try:
+        from opt_ring_flash_attn_b200.transport import RingTransport
+
+        t = RingTransport(None, torch.device("cpu"))
+        with pytest.raises(RuntimeError):
+            t.wait()
+        buf = torch.zeros(4)
+        with pytest.raises(RuntimeError):
+            t.post(buf, buf)
+    finally:
+        dist.destroy_process_group()
