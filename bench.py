@@ -211,8 +211,8 @@ def cpu_baseline_leg(cfg, budget_s=20.0):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -261,13 +261,13 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(warmup):
-        step_device()
-    barrier()
-
+    # clocks are sampled from the warm-up on, so that short timed regions still get samples under load
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(warmup):
+        step_device()
+    barrier()
     launches0 = _native.launch_count()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
@@ -368,7 +368,6 @@ def main():
         e2e_ms = float(te.item())
         h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv, hdo))
         d2h = sum(x.numel() * x.element_size() for x in (h_out, h_dq, h_dk, h_dv))
-    status_ok = True
     for ws in list(workspace._fwd_cache.values()) + list(workspace._bwd_cache.values()):
         _native.check_status(ws.status, "bench")
 

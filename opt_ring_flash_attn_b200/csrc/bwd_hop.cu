@@ -203,53 +203,58 @@ __global__ void __launch_bounds__(512, 1)
       const uint32_t tm_dv = tmem_base + Cfg::kTmDV;
       const uint32_t tm_dk = tmem_base + Cfg::kTmDK;
 
+      // Descriptor low words of the resident tiles; offsets below are in 16-byte units.
+      const uint32_t k_km = desc_lo_kmajor(s_k);                                   // K as K-major A (S^T)
+      const uint32_t v_km = desc_lo_kmajor(s_v);                                   // V as K-major A (dP^T)
+      const uint32_t k_mn = desc_lo_mnmajor(s_k + hf * (DH / 64) * kPanelK, kPanelK);  // K^T as MN-major A (dQ^T)
+      const uint32_t ds_km = desc_lo_kmajor(s_ds);                                 // dS^T as K-major A (dK)
+      const uint32_t ds_mn = desc_lo_mnmajor(s_ds, kPanelK);                       // dS^T as MN-major B (dQ^T)
+      auto q_km = [&](int st) { return desc_lo_kmajor(s_q + st * Cfg::kQBytes); };
+      auto do_km = [&](int st) { return desc_lo_kmajor(s_do + st * Cfg::kQBytes); };
+      auto q_mn = [&](int st) { return desc_lo_mnmajor(s_q + st * Cfg::kQBytes + hf * (DH / 64) * kPanelQ, kPanelQ); };
+      auto do_mn = [&](int st) { return desc_lo_mnmajor(s_do + st * Cfg::kQBytes + hf * (DH / 64) * kPanelQ, kPanelQ); };
+
       // S^T[128 x BQ] = K[128 x DP] * Q[BQ x DP]^T
       auto issue_s = [&](int st) {
+        const uint32_t bq = q_km(st);
 #pragma unroll
-        for (int ks = 0; ks < DP / 16; ++ks) {
-          const uint32_t a = s_k + (ks >> 2) * kPanelK + (ks & 3) * 32;
-          const uint32_t bq = s_q + st * Cfg::kQBytes + (ks >> 2) * kPanelQ + (ks & 3) * 32;
-          mma_ss(tm_s, desc_kmajor(a), desc_kmajor(bq), idesc_s, ks > 0 ? 1u : 0u);
-        }
+        for (int ks = 0; ks < DP / 16; ++ks)
+          mma_ss_lo(tm_s, k_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4),
+                    bq + (((ks >> 2) * kPanelQ + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u);
       };
       // dP^T[128 x BQ] = V[128 x DP] * dO[BQ x DP]^T
       auto issue_dp = [&](int st) {
+        const uint32_t bo = do_km(st);
 #pragma unroll
-        for (int ks = 0; ks < DP / 16; ++ks) {
-          const uint32_t a = s_v + (ks >> 2) * kPanelK + (ks & 3) * 32;
-          const uint32_t bo = s_do + st * Cfg::kQBytes + (ks >> 2) * kPanelQ + (ks & 3) * 32;
-          mma_ss(tm_dp, desc_kmajor(a), desc_kmajor(bo), idesc_s, ks > 0 ? 1u : 0u);
-        }
+        for (int ks = 0; ks < DP / 16; ++ks)
+          mma_ss_lo(tm_dp, v_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4),
+                    bo + (((ks >> 2) * kPanelQ + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u);
       };
       // dV[128 x DH] += P^T[128 x BQ] (tensor memory) * dO[BQ x DH]
       auto issue_dv = [&](int st, bool acc) {
+        const uint32_t bo = do_mn(st);
 #pragma unroll
         for (int ks = 0; ks < BQ / 16; ++ks) {
-          const uint32_t bo = s_do + st * Cfg::kQBytes + hf * (DH / 64) * kPanelQ + ks * 2048;
           // P^T of query columns [16ks, 16ks+16): each elementwise group packs its half over its own S^T columns
           const int grp = (ks * 16) / (BQ / 2);
           const uint32_t pa = tm_s + grp * (BQ / 2) + ((ks * 16) % (BQ / 2)) / 2;
-          mma_ts(tm_dv, pa, desc_mnmajor(bo, kPanelQ), idesc_dv, (acc || ks > 0) ? 1u : 0u);
+          mma_ts_lo(tm_dv, pa, bo + ((ks * 2048) >> 4), idesc_dv, (acc || ks > 0) ? 1u : 0u);
         }
       };
       // dK[128 x DH] += dS^T[128 x BQ] (shared memory, K-major) * Q[BQ x DH]
       auto issue_dk = [&](int st, bool acc) {
+        const uint32_t bq = q_mn(st);
 #pragma unroll
-        for (int ks = 0; ks < BQ / 16; ++ks) {
-          const uint32_t a = s_ds + (ks >> 2) * kPanelK + (ks & 3) * 32;
-          const uint32_t bq = s_q + st * Cfg::kQBytes + hf * (DH / 64) * kPanelQ + ks * 2048;
-          mma_ss(tm_dk, desc_kmajor(a), desc_mnmajor(bq, kPanelQ), idesc_dv, (acc || ks > 0) ? 1u : 0u);
-        }
+        for (int ks = 0; ks < BQ / 16; ++ks)
+          mma_ss_lo(tm_dk, ds_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4), bq + ((ks * 2048) >> 4), idesc_dv,
+                    (acc || ks > 0) ? 1u : 0u);
       };
       // dQ^T[128 (d) x BQ] = K^T[d x 128 (kv)] * dS^T[128 (kv) x BQ]; for head dim 64 the upper 64
       // rows of the A operand run into the V tile (results in those lanes are ignored).
       auto issue_dq = [&]() {
 #pragma unroll
-        for (int ks = 0; ks < 128 / 16; ++ks) {
-          const uint32_t a = s_k + hf * (DH / 64) * kPanelK + ks * 2048;
-          const uint32_t bs = s_ds + ks * 2048;
-          mma_ss(tm_dp, desc_mnmajor(a, kPanelK), desc_mnmajor(bs, kPanelK), idesc_dq, ks > 0 ? 1u : 0u);
-        }
+        for (int ks = 0; ks < 128 / 16; ++ks)
+          mma_ss_lo(tm_dp, k_mn + ((ks * 2048) >> 4), ds_mn + ((ks * 2048) >> 4), idesc_dq, ks > 0 ? 1u : 0u);
       };
 
       bool ok = mbar_wait(&bar_kv_full, 0, abort_p);

@@ -33,6 +33,8 @@ struct FwdParams {
   float scale_log2;
   int first, last, causal;
   int* status;
+  unsigned long long* trace;
+  int trace_ctas, trace_cap;
 };
 
 template <int DP, int BN, int NQ, int NS>
@@ -56,9 +58,9 @@ template <int DP, int BN>
 __device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_smem, uint32_t k_smem, uint32_t idesc) {
 #pragma unroll
   for (int ks = 0; ks < DP / 16; ++ks) {
-    const uint32_t a = q_smem + (ks >> 2) * (128 * 128) + (ks & 3) * 32;
-    const uint32_t b = k_smem + (ks >> 2) * (BN * 128) + (ks & 3) * 32;
-    mma_ss(s_tmem, desc_kmajor(a), desc_kmajor(b), idesc, ks > 0 ? 1u : 0u);
+    // q_smem / k_smem are descriptor low words of the tile bases; offsets are in 16-byte units
+    mma_ss_lo(s_tmem, q_smem + (((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4),
+              k_smem + (((ks >> 2) * (BN * 128) + (ks & 3) * 32) >> 4), idesc, ks > 0 ? 1u : 0u);
   }
 }
 
@@ -68,8 +70,7 @@ __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint3
                                          bool accumulate) {
 #pragma unroll
   for (int ks = 0; ks < BN / 16; ++ks) {
-    mma_ts(o_tmem, p_tmem + ks * 8, desc_mnmajor(v_smem + ks * 2048, BN * 128), idesc,
-           (accumulate || ks > 0) ? 1u : 0u);
+    mma_ts_lo(o_tmem, p_tmem + ks * 8, v_smem + ((ks * 2048) >> 4), idesc, (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
@@ -149,6 +150,12 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_holder;
   volatile int* abort_p = &abort_flag;
+  Tracer tr;
+  {
+    int role = -1;
+    if (lane == 0) role = (warp == 0) ? 0 : (warp == 1) ? 1 : (warp == 4) ? 2 : (warp == 8) ? 3 : -1;
+    if (role >= 0) tr.init(p.trace, p.trace_ctas, p.trace_cap, kTraceRoles, role);
+  }
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
@@ -179,6 +186,7 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
             ok = false;
             break;
           }
+          tr.mark(40 + which);
           mbar_expect_tx(&bar_kv_full[slot], Cfg::kKVBytes);
 #pragma unroll
           for (int pn = 0; pn < Cfg::kPanels; ++pn)
@@ -195,7 +203,12 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
       constexpr uint32_t idesc_pv = make_idesc(128, DP, kBf16, false, true);
       auto slot_of = [&](int u) { return u % kSlots; };
       auto par_of = [&](int u) { return static_cast<uint32_t>((u / kSlots) & 1); };
-      auto kv_addr = [&](int u) { return s_kv + slot_of(u) * Cfg::kKVBytes; };
+      // descriptor low words of the operand tiles (K: K-major, V: MN-major, Q: K-major)
+      auto k_lo = [&](int u) { return desc_lo_kmajor(s_kv + slot_of(u) * Cfg::kKVBytes); };
+      auto v_lo = [&](int u) { return desc_lo_mnmajor(s_kv + slot_of(u) * Cfg::kKVBytes, BN * 128); };
+      uint32_t q_lo[NQ];
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) q_lo[q] = desc_lo_kmajor(s_q + q * Cfg::kQBytes);
       auto s_tm = [&](int q, int sb) { return tmem_base + Cfg::kTmS + (q * NS + sb) * BN; };
       auto o_tm = [&](int q) { return tmem_base + Cfg::kTmO + q * DP; };
       bool ok = nmax > 0;
@@ -206,7 +219,7 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
           if (ntile[q] > 0) {
-            issue_qk<DP, BN>(s_tm(q, 0), s_q + q * Cfg::kQBytes, kv_addr(0), idesc_qk);
+            issue_qk<DP, BN>(s_tm(q, 0), q_lo[q], k_lo(0), idesc_qk);
             mma_commit(&bar_s_full[q * NS + 0]);
           }
         }
@@ -219,29 +232,33 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
             const int uk = 2 * (j + 1);
             if (!mbar_wait(&bar_kv_full[slot_of(uk)], par_of(uk), abort_p)) { ok = false; break; }
             tc_fence_after_sync();
-            issue_qk<DP, BN>(s_tm(0, (j + 1) & 1), s_q, kv_addr(uk), idesc_qk);
+            issue_qk<DP, BN>(s_tm(0, (j + 1) & 1), q_lo[0], k_lo(uk), idesc_qk);
             mma_commit(&bar_s_full[(j + 1) & 1]);
             mma_commit(&bar_kv_empty[slot_of(uk)]);
           }
         }
         const int uv = 2 * j + 1;
+        tr.mark(9);
         if (!mbar_wait(&bar_kv_full[slot_of(uv)], par_of(uv), abort_p)) { ok = false; break; }
+        tr.mark(10);
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
           if (j < ntile[q]) {
             const int sb = (NS == 2) ? (j & 1) : 0;
             const uint32_t par = (NS == 2) ? ((j >> 1) & 1) : (j & 1);
             if (!mbar_wait(&bar_p_ready[q * NS + sb], par, abort_p)) { ok = false; break; }
+            tr.mark(11 + 2 * q);
             tc_fence_after_sync();
-            issue_pv<DP, BN>(o_tm(q), s_tm(q, sb), kv_addr(uv), idesc_pv, (j > 0) || (p.first == 0));
+            issue_pv<DP, BN>(o_tm(q), s_tm(q, sb), v_lo(uv), idesc_pv, (j > 0) || (p.first == 0));
             mma_commit(&bar_pv_done[q]);
             if (NS == 1 && j + 1 < ntile[q]) {
               const int uk = 2 * (j + 1);
               if (!mbar_wait(&bar_kv_full[slot_of(uk)], par_of(uk), abort_p)) { ok = false; break; }
               tc_fence_after_sync();
-              issue_qk<DP, BN>(s_tm(q, 0), s_q + q * Cfg::kQBytes, kv_addr(uk), idesc_qk);
+              issue_qk<DP, BN>(s_tm(q, 0), q_lo[q], k_lo(uk), idesc_qk);
               mma_commit(&bar_s_full[q * NS + 0]);
             }
+            tr.mark(12 + 2 * q);
           }
         }
         if (!ok) break;
@@ -293,7 +310,9 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
       for (int j = 0; j < n; ++j) {
         const int sb = (NS == 2) ? (j & 1) : 0;
         const uint32_t par = (NS == 2) ? ((j >> 1) & 1) : (j & 1);
+        tr.mark(19);
         if (!mbar_wait_warp(&bar_s_full[q * NS + sb], par, abort_p)) { ok = false; break; }
+        tr.mark(20);
         tc_fence_after_sync();
         const uint32_t s_addr = tmem_base + lane_addr + Cfg::kTmS + (q * NS + sb) * BN;
         const int n0 = j * BN;
@@ -316,6 +335,7 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
           }
         }
         const float m_new = fmaxf(m_used, mx * p.scale_log2);
+        tr.mark(21);
 
         // lazy rescale: only when the maximum grew by more than 2^8
         bool need;
@@ -343,6 +363,7 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
             tmem_st32(o_addr + c * 32, r);
           }
           tmem_st_wait();
+          tr.mark(23);
         }
 
         // pass 2: P = exp2(s * scale_log2 - m_used), packed to 16 bit over the start of S
@@ -366,9 +387,11 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
           }
           tmem_st16(s_addr + c * 16, u);
         }
+        tr.mark(24);
         tmem_st_wait();
         tc_fence_before_sync();
         mbar_arrive(&bar_p_ready[q * NS + sb]);
+        tr.mark(25);
       }
 
       // ---- epilogue: wait for the last PV, then spill state or write the result ----
@@ -514,6 +537,9 @@ extern "C" int rfa_fwd_hop(const void* q, const void* k, const void* v, float* a
   prm.last = last ? 1 : 0;
   prm.causal = causal_diag ? 1 : 0;
   prm.status = status;
+  prm.trace = g_trace.buf;
+  prm.trace_ctas = g_trace.ctas;
+  prm.trace_cap = g_trace.cap;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == RFA_DTYPE_BF16) return dispatch_fwd<__nv_bfloat16>(dp, q, k, v, prm, dtype, s);
   return dispatch_fwd<__half>(dp, q, k, v, prm, dtype, s);
