@@ -56,22 +56,22 @@ struct FwdCfg {
 // S[128 x BN] = Q[128 x DP] * K[BN x DP]^T, both operands K-major.
 template <int DP, int BN>
 __device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_smem, uint32_t k_smem, uint32_t idesc) {
-#pragma unroll
-  for (int ks = 0; ks < DP / 16; ++ks) {
-    // q_smem / k_smem are descriptor low words of the tile bases; offsets are in 16-byte units
-    mma_ss_lo(s_tmem, q_smem + (((ks >> 2) * (128 * 128) + (ks & 3) * 32) >> 4),
-              k_smem + (((ks >> 2) * (BN * 128) + (ks & 3) * 32) >> 4), idesc, ks > 0 ? 1u : 0u);
-  }
+  // q_smem / k_smem are descriptor low words of the tile bases; offsets are in 16-byte units
+  static_for<0, DP / 16>([&](auto ks_) {
+    constexpr int ks = decltype(ks_)::value;
+    mma_ss_off<(((ks / 4) * (128 * 128) + (ks % 4) * 32) / 16), (((ks / 4) * (BN * 128) + (ks % 4) * 32) / 16)>(
+        s_tmem, q_smem, k_smem, idesc, ks > 0 ? 1u : 0u);
+  });
 }
 
 // O[128 x DP] (+)= P[128 x BN] * V[BN x DP]; P in tensor memory, V MN-major.
 template <int DP, int BN>
 __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint32_t v_smem, uint32_t idesc,
                                          bool accumulate) {
-#pragma unroll
-  for (int ks = 0; ks < BN / 16; ++ks) {
-    mma_ts_lo(o_tmem, p_tmem + ks * 8, v_smem + ((ks * 2048) >> 4), idesc, (accumulate || ks > 0) ? 1u : 0u);
-  }
+  static_for<0, BN / 16>([&](auto ks_) {
+    constexpr int ks = decltype(ks_)::value;
+    mma_ts_off<(ks * 8), (ks * 128)>(o_tmem, p_tmem, v_smem, idesc, (accumulate || ks > 0) ? 1u : 0u);
+  });
 }
 
 template <int DP, int BN, int NQ, int NS, typename T>
@@ -318,22 +318,37 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
         const int n0 = j * BN;
         const bool masked = (p.causal && (n0 + BN - 1 > m0[q])) || (n0 + BN > p.Skv);
 
-        // pass 1: row maximum of the raw scores
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(s_addr + c * 32, r);
-          tmem_ld_wait32(r);
-          if (masked) {
+        // The whole score row (BN fp32 values) goes to registers in one batch of loads.
+        constexpr int NCH = BN / 32;
+        uint32_t r[NCH][32];
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) tmem_ld32(s_addr + c * 32, r[c]);
+        tmem_ld_wait32(r[0]);
+#pragma unroll
+        for (int c = 1; c < NCH; ++c) reg_fence32(r[c]);
+        if (masked) {
+          // keys beyond the causal limit of this row / beyond the end of the block count as -inf
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if (n0 + c * 32 + i <= col_lim) mx = fmaxf(mx, __uint_as_float(r[i]));
-          } else {
+              if (n0 + c * 32 + i > col_lim) r[c][i] = __float_as_uint(-INFINITY);
+        }
+        // row maximum of the raw scores (independent partial maxima keep the dependency chains short)
+        float mxp[NCH][2];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int c = 0; c < NCH; ++c) {
+          mxp[c][0] = __uint_as_float(r[c][0]);
+          mxp[c][1] = __uint_as_float(r[c][1]);
+#pragma unroll
+          for (int i = 2; i < 32; i += 2) {
+            mxp[c][0] = fmaxf(mxp[c][0], __uint_as_float(r[c][i]));
+            mxp[c][1] = fmaxf(mxp[c][1], __uint_as_float(r[c][i + 1]));
           }
         }
+        float mx = fmaxf(mxp[0][0], mxp[0][1]);
+#pragma unroll
+        for (int c = 1; c < NCH; ++c) mx = fmaxf(mx, fmaxf(mxp[c][0], mxp[c][1]));
         const float m_new = fmaxf(m_used, mx * p.scale_log2);
         tr.mark(21);
 
@@ -354,39 +369,35 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
             tc_fence_after_sync();
           }
 #pragma unroll 1
-          for (int c = 0; c < DP / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32(o_addr + c * 32, r);
-            tmem_ld_wait32(r);
+          for (int c = 0; c < DP / 16; ++c) {
+            uint32_t o16[16];
+            tmem_ld16(o_addr + c * 16, o16);
+            tmem_ld_wait16(o16);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(o_addr + c * 32, r);
+            for (int i = 0; i < 16; ++i) o16[i] = __float_as_uint(__uint_as_float(o16[i]) * alpha);
+            tmem_st16(o_addr + c * 16, o16);
           }
           tmem_st_wait();
           tr.mark(23);
         }
 
-        // pass 2: P = exp2(s * scale_log2 - m_used), packed to 16 bit over the start of S
+        // P = exp2(s * scale_log2 - m_used), packed to 16 bit over the start of S
         const float neg_m = -m_used;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(s_addr + c * 32, r);
-          tmem_ld_wait32(r);
+        float lp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
           uint32_t u[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            float p0 = fast_exp2(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, neg_m));
-            float p1 = fast_exp2(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, neg_m));
-            if (masked) {
-              if (n0 + c * 32 + 2 * i > col_lim) p0 = 0.f;
-              if (n0 + c * 32 + 2 * i + 1 > col_lim) p1 = 0.f;
-            }
-            l_sum += p0 + p1;
+            const float p0 = fast_exp2(fmaf(__uint_as_float(r[c][2 * i]), p.scale_log2, neg_m));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(r[c][2 * i + 1]), p.scale_log2, neg_m));
+            lp[(2 * i) & 3] += p0;
+            lp[(2 * i + 1) & 3] += p1;
             u[i] = Pack2<T>::pack(p0, p1);
           }
           tmem_st16(s_addr + c * 16, u);
         }
+        l_sum += (lp[0] + lp[1]) + (lp[2] + lp[3]);
         tr.mark(24);
         tmem_st_wait();
         tc_fence_before_sync();
