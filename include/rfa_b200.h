@@ -109,6 +109,15 @@ int rfa_bwd_hop(const void* q, const void* k, const void* v, const void* dout, c
                 void* stream);
 
 /*
+ * out[i] = prev[i] + block[i] for n fp32 elements (n % 4 == 0; out may alias prev or block).
+ * The ring accumulate of the travelling dK/dV buffer as a kernel of its own, for schedules that launch the
+ * backward hop before the previous rank's partial sums have arrived (the hop then runs with
+ * accumulate_prev = 0 into a block buffer, and this kernel folds the block in once the receive completed).
+ * Replaces `_dkdv_accum_kernel` / `_launch_dkdv_accum` (optimized_ring_flash_attn.py:476-503, 1007-1012).
+ */
+int rfa_dkdv_accumulate(const float* prev, const float* block, float* out, size_t n, void* stream);
+
+/*
  * rfa_bwd_hop for callers that cannot allocate device memory (no counterpart in the reference).
  *
  * Same computation as rfa_bwd_hop followed by rfa_bwd_dq_finalize, but the caller passes no dQ

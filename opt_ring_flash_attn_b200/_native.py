@@ -41,6 +41,7 @@ SIGNATURES = {
     "rfa_bwd_hop": (_i, [_vp] * 9 + [_i] * 7 + [_f] + [_i] * 2 + [_vp, _vp]),
     "rfa_noalloc_scratch_bytes": (_sz, []),
     "rfa_bwd_hop_noalloc": (_i, [_vp] * 9 + [_i] * 7 + [_f] + [_i] * 2 + [_vp, _vp]),
+    "rfa_dkdv_accumulate": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "rfa_cast_from_f32": (_i, [_vp, _vp, _sz, _i, _vp]),
     "rfa_pack_kv": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "rfa_debug_mma_probe": (_i, [_i, _vp, _vp, _vp, _vp, _vp]),
@@ -164,6 +165,12 @@ def dq_finalize(dq_acc: torch.Tensor, dq: torch.Tensor, stream=None) -> None:
     B, Sq, Hq, D = dq.shape
     rc = load().rfa_bwd_dq_finalize(_ptr(dq_acc), _ptr(dq), B, Sq, Hq, D, DTYPE_CODES[dq.dtype], _stream(stream))
     _check(rc, "rfa_bwd_dq_finalize")
+
+
+def dkdv_accumulate(prev: torch.Tensor, block: torch.Tensor, out: torch.Tensor, stream=None) -> None:
+    assert prev.dtype == block.dtype == out.dtype == torch.float32 and prev.numel() == block.numel() == out.numel()
+    rc = load().rfa_dkdv_accumulate(_ptr(prev), _ptr(block), _ptr(out), prev.numel(), _stream(stream))
+    _check(rc, "rfa_dkdv_accumulate")
 
 
 def cast_from_f32(src: torch.Tensor, dst: torch.Tensor, stream=None) -> None:

@@ -173,6 +173,18 @@ __global__ void __launch_bounds__(256) dq_finalize_kernel(const float* __restric
   }
 }
 
+// out = a + b over n4 float4 elements (out may alias a or b): the ring accumulate of the partial dK/dV.
+// Streams 3 * 16 bytes per element: HBM-bound.
+__global__ void __launch_bounds__(256) add_f32_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
+                                                     float4* out, size_t n4) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 x = a[i];
+    const float4 y = b[i];
+    out[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) cast_from_f32_kernel(const float* __restrict__ src, T* __restrict__ dst,
                                                            size_t n8, size_t n) {
@@ -264,6 +276,22 @@ extern "C" int rfa_bwd_dq_finalize(const float* dq_acc, void* dq, int B, int Sq,
     dq_finalize_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), B, Sq, Hq, D, dp, nQt);
   else
     dq_finalize_kernel<__half><<<grid, 256, 0, s>>>(dq_acc, static_cast<__half*>(dq), B, Sq, Hq, D, dp, nQt);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" int rfa_dkdv_accumulate(const float* prev, const float* block, float* out, size_t n, void* stream) {
+  using namespace rfa;
+  if (!prev || !block || !out) return RFA_ERR_INVALID_ARG;
+  if ((n & 3u) != 0) return RFA_ERR_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(prev) & 15u) || (reinterpret_cast<uintptr_t>(block) & 15u) ||
+      (reinterpret_cast<uintptr_t>(out) & 15u))
+    return RFA_ERR_INVALID_ARG;
+  if (n == 0) return RFA_OK;
+  const size_t n4 = n / 4;
+  size_t blocks = (n4 + 255) / 256;
+  if (blocks > 148u * 16) blocks = 148u * 16;
+  add_f32_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float4*>(prev), reinterpret_cast<const float4*>(block), reinterpret_cast<float4*>(out), n4);
   return cuda_status(cudaGetLastError());
 }
 

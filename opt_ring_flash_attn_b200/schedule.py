@@ -8,7 +8,9 @@ its own block (step 0), and its result is final at ``step == rank``.
 Backward follows ``_ring_backward_native`` (optimized_ring_flash_attn.py:946-1029):
 a second ring carries the fp32 partial dK/dV of the block a rank currently
 holds; slot algebra ``prev_slot = (step - 1) & 1``, the W-th send returns the
-sums to the block's owner (``final_slot = (W - 1) & 1``).
+sums to the block's owner (``final_slot = (W - 1) & 1``).  As in the reference, the hop kernel of a step
+is launched before the partial sums of the previous rank are waited for, and a separate accumulate kernel
+folds them in (optimized_ring_flash_attn.py:1001-1012), so the large kernel never waits on the ring.
 
 Differences from the reference, on purpose: a world size of 1 runs with no
 communication at all; the fp32 running state replaces the per-hop merge kernel;
@@ -107,11 +109,16 @@ def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
             kv_comm.post(cur, ws.kv_recv[step & 1])
         prev_slot = (step - 1) & 1
         buf = ws.dkdv[prev_slot]
+        active = (not causal) or step <= rank
+        if active:
+            # The hop kernel does not wait for the ring: on step 0 it writes the travelling buffer directly,
+            # later it writes this rank's block and the partial sums are folded in once they have arrived.
+            kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, buf if step == 0 else ws.block_dkdv,
+                       softmax_scale, False, causal and step == 0, ws.status)
         if step > 0:
             dkv_comm.wait()  # partial dK/dV of the block now held has arrived in dkdv[prev_slot]
-        if (not causal) or step <= rank:
-            kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, buf if step > 0 else None, buf,
-                       softmax_scale, step > 0, causal and step == 0, ws.status)
+            if active:
+                kn.dkdv_accumulate(buf, ws.block_dkdv, buf)
         if step + 1 < W:
             kv_comm.wait()
             cur = ws.kv_recv[step & 1]

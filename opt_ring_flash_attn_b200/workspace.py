@@ -40,6 +40,7 @@ class BackwardWorkspace:
     lse2: torch.Tensor                # fp32 [B, Hq, Spad]
     dq_acc: torch.Tensor              # fp32, private tiled layout (B*Hq*Spad*padded D elements)
     dkdv: List[torch.Tensor]          # 2 x fp32 [2, B, S, Hkv, D] (1 slot when world size is 1)
+    block_dkdv: Optional[torch.Tensor]  # fp32 [2, B, S, Hkv, D]: this hop's own dK/dV before the ring accumulate
     kv_send: Optional[torch.Tensor]
     kv_recv: List[torch.Tensor]
     status: torch.Tensor
@@ -92,12 +93,13 @@ def backward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int) -> Bac
     nslots = 1 if world_size == 1 else 2
     dkdv = [torch.empty(2, B, S, Hkv, D, dtype=torch.float32, device=dev) for _ in range(nslots)]
     if world_size == 1:
-        kv_send, kv_recv = None, []
+        kv_send, kv_recv, block_dkdv = None, [], None
     else:
         kv_send = torch.empty(2, B, S, Hkv, D, dtype=q.dtype, device=dev)
         kv_recv = [torch.empty_like(kv_send) for _ in range(2)]
+        block_dkdv = torch.empty_like(dkdv[0])
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    ws = BackwardWorkspace(delta, lse2, dq_acc, dkdv, kv_send, kv_recv, status)
+    ws = BackwardWorkspace(delta, lse2, dq_acc, dkdv, block_dkdv, kv_send, kv_recv, status)
     _bwd_cache.clear()
     _bwd_cache[key] = ws
     return ws

@@ -96,5 +96,9 @@ def dq_finalize(dq_acc, dq, stream=None):
     dq.copy_(dq_acc[: B * Hq * S * D].view(B, Hq, S, D).transpose(1, 2).to(dq.dtype))
 
 
+def dkdv_accumulate(prev, block, out, stream=None):
+    out.copy_(prev + block)
+
+
 def cast_from_f32(src, dst, stream=None):
     dst.copy_(src.to(dst.dtype))

@@ -134,6 +134,20 @@ def test_run_twice_bitwise_forward():
         assert torch.equal(a, b)
 
 
+def test_dkdv_accumulate():
+    from opt_ring_flash_attn_b200 import _native
+
+    dev = torch.device("cuda:0")
+    a = torch.randn(2, 1, 200, 2, 96, device=dev)
+    b = torch.randn_like(a)
+    out = torch.empty_like(a)
+    _native.dkdv_accumulate(a, b, out)
+    assert torch.equal(out, a + b)
+    ref = a + b
+    _native.dkdv_accumulate(a, b, a)  # in place, as the ring schedule uses it
+    assert torch.equal(a, ref)
+
+
 def test_abi_rejects_bad_arguments():
     from opt_ring_flash_attn_b200 import _native
 
