@@ -21,6 +21,8 @@
 // the dV / dK epilogues), warps 12-15 dQ reduction.
 // Tensor memory: [0,BQ) S^T / P^T, [BQ,2BQ) dP^T then dQ^T, then dV (DH) and dK (DH).
 // Head dim 256 runs as two CTAs per tile, each owning 128 columns of dK, dV, dQ.
+#include <stdlib.h>
+
 #include <type_traits>
 
 #include "common.h"
@@ -38,6 +40,8 @@ struct BwdParams {
   int Spad;
   float scale, scale_log2;
   int accumulate_prev, causal;
+  int gsplit;      // CTAs per (kv tile, kv head): each takes G / gsplit query heads of the group
+  int reduce_out;  // 1: the epilogue adds into dkdv_out with vector reductions (gsplit > 1); 0: plain stores
   int* status;
   unsigned long long* trace;
   int trace_ctas, trace_cap;
@@ -103,19 +107,22 @@ __global__ void __launch_bounds__(512, 1)
   uint8_t* const ds_ptr = smem_raw + Cfg::kOffDS;
 
   // ---- tile coordinates: kv tiles with the most visible queries first ----
-  const int per_kvt = p.Hkv * p.B * Cfg::kHalves;
+  const int per_kvt = p.Hkv * p.B * Cfg::kHalves * p.gsplit;
   const int kvt = static_cast<int>(blockIdx.x) / per_kvt;
   int rem = static_cast<int>(blockIdx.x) % per_kvt;
   const int hf = rem % Cfg::kHalves;
   rem /= Cfg::kHalves;
+  const int gs = rem % p.gsplit;  // CTAs that share a K/V tile are adjacent (the tile stays in L2)
+  rem /= p.gsplit;
   const int hkv = rem % p.Hkv;
   const int b = rem / p.Hkv;
   const int G = p.Hq / p.Hkv;
+  const int Gc = G / p.gsplit;
   const int n0 = kvt * 128;
   const int nQtiles = (p.Sq + BQ - 1) / BQ;
   const int i_begin = p.causal ? (n0 / BQ) : 0;
   const int nI = nQtiles - i_begin;
-  const int T_total = G * nI;
+  const int T_total = Gc * nI;
 
   if (tid == 0) {
     abort_flag = ((smem_base & 1023u) != 0) ? 1 : 0;  // operand tiles need 1024-byte alignment
@@ -152,7 +159,7 @@ __global__ void __launch_bounds__(512, 1)
     if (lane == 0) role = (warp == 0) ? 0 : (warp == 1) ? 1 : (warp == 4) ? 2 : (warp == 8) ? 3 : (warp == 12) ? 4 : -1;
     if (role >= 0) tr.init(p.trace, p.trace_ctas, p.trace_cap, kTraceRoles, role);
   }
-  auto q_head = [&](int t) { return hkv * G + t / nI; };
+  auto q_head = [&](int t) { return hkv * G + gs * Gc + t / nI; };
   auto q_tile = [&](int t) { return i_begin + t % nI; };
 
   if (warp == 0) {
@@ -459,11 +466,16 @@ __global__ void __launch_bounds__(512, 1)
             if (d < p.D) {
               float4 v = make_float4(__uint_as_float(r[4 * k + 0]) * mul, __uint_as_float(r[4 * k + 1]) * mul,
                                      __uint_as_float(r[4 * k + 2]) * mul, __uint_as_float(r[4 * k + 3]) * mul);
-              if (p.accumulate_prev) {
-                const float4 o = *reinterpret_cast<const float4*>(p.dkdv_prev + base + c * 32 + k * 4);
-                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              if (p.reduce_out) {
+                // several CTAs (one per slice of the GQA group) add into the same rows; the host prepared dkdv_out
+                red_add_v4_f32(p.dkdv_out + base + c * 32 + k * 4, v.x, v.y, v.z, v.w);
+              } else {
+                if (p.accumulate_prev) {
+                  const float4 o = *reinterpret_cast<const float4*>(p.dkdv_prev + base + c * 32 + k * 4);
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *reinterpret_cast<float4*>(p.dkdv_out + base + c * 32 + k * 4) = v;
               }
-              *reinterpret_cast<float4*>(p.dkdv_out + base + c * 32 + k * 4) = v;
             }
           }
         }
@@ -556,8 +568,40 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
     if (e != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
     attr_done = true;
   }
-  const unsigned grid = static_cast<unsigned>(ceil_div(prm.Skv, 128)) * prm.Hkv * prm.B * Cfg::kHalves;
-  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, tdo, prm);
+  // Work units: one CTA per (kv tile, kv head, batch, head-dim half).  With 148 SMs and one CTA per SM a grid that is
+  // not close to a multiple of 148 wastes the last wave, so a GQA group may be split over several CTAs whose partial
+  // dK/dV are added with vector reductions.  Pick the smallest split that fills the waves to >= 90 %.
+  BwdParams pr = prm;
+  const int G = prm.Hq / prm.Hkv;
+  const long long base_units = static_cast<long long>(ceil_div(prm.Skv, 128)) * prm.Hkv * prm.B * Cfg::kHalves;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int gsplit = 1; gsplit <= G; ++gsplit) {
+    if (G % gsplit) continue;
+    const long long units = base_units * gsplit;
+    const double eff = static_cast<double>(units) / static_cast<double>((units + 147) / 148 * 148);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = gsplit; }
+    if (eff >= 0.9) { best = gsplit; break; }
+  }
+  {
+    // Tuning override (diagnostics): RFA_B200_BWD_GSPLIT=<divisor of the group size> forces the split.
+    static const int forced = [] { const char* e = getenv("RFA_B200_BWD_GSPLIT"); return e ? atoi(e) : 0; }();
+    if (forced > 0 && G % forced == 0) best = forced;
+  }
+  pr.gsplit = best;
+  pr.reduce_out = best > 1 ? 1 : 0;
+  if (pr.reduce_out) {
+    const size_t bytes = static_cast<size_t>(2) * prm.B * prm.Skv * prm.Hkv * prm.D * sizeof(float);
+    cudaError_t e = cudaSuccess;
+    if (prm.accumulate_prev) {
+      if (prm.dkdv_prev != prm.dkdv_out) e = cudaMemcpyAsync(prm.dkdv_out, prm.dkdv_prev, bytes, cudaMemcpyDeviceToDevice, stream);
+    } else {
+      e = cudaMemsetAsync(prm.dkdv_out, 0, bytes, stream);
+    }
+    if (e != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
+  }
+  const unsigned grid = static_cast<unsigned>(base_units * pr.gsplit);
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, tdo, pr);
   return cuda_status(cudaGetLastError());
 }
 
@@ -607,6 +651,8 @@ extern "C" int rfa_bwd_hop(const void* q, const void* k, const void* v, const vo
   prm.scale_log2 = softmax_scale * 1.4426950408889634f;
   prm.accumulate_prev = accumulate_prev ? 1 : 0;
   prm.causal = causal_diag ? 1 : 0;
+  prm.gsplit = 1;
+  prm.reduce_out = 0;
   prm.status = status;
   prm.trace = g_trace.buf;
   prm.trace_ctas = g_trace.ctas;
