@@ -96,37 +96,39 @@ __global__ void __launch_bounds__(256) bwd_prepare_kernel(const T* __restrict__ 
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < dq_vec4; i += stride)
       reinterpret_cast<float4*>(dq_acc)[i] = z;
   }
+  // A row of D 16-bit values is D/8 16-byte vectors; a group of gsz lanes (gsz = 4, 8, 16 or 32, the
+  // power of two >= D/8) owns one row, so a warp streams 32/gsz rows at a time with every lane loading.
+  const int vec_per_row = D / 8;
+  int gsz = 4;
+  while (gsz < vec_per_row) gsz <<= 1;
   const int lane = threadIdx.x & 31;
+  const int sub = lane / gsz;            // row slot inside the warp
+  const int gl = lane % gsz;             // lane inside the group
+  const int rows_per_warp = 32 / gsz;
   const long long warp_global = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const long long rows = static_cast<long long>(B) * Spad * Hq;
-  const int vec_per_row = D / 8;  // 16-byte vectors of 16-bit elements
-  for (long long r = warp_global; r < rows; r += nwarps) {
-    // r enumerates (b, s, h) with h fastest so that consecutive warps stream consecutive memory.
-    const int h = static_cast<int>(r % Hq);
-    const long long bs = r / Hq;
+  for (long long r0 = warp_global * rows_per_warp; r0 < rows; r0 += nwarps * rows_per_warp) {
+    // rows are enumerated (b, s, h) with h fastest so that consecutive groups stream consecutive memory
+    const long long r = r0 + sub;
+    const bool in_range = r < rows;
+    const int h = in_range ? static_cast<int>(r % Hq) : 0;
+    const long long bs = in_range ? r / Hq : 0;
     const int s = static_cast<int>(bs % Spad);
     const int b = static_cast<int>(bs / Spad);
     const size_t stat = (static_cast<size_t>(b) * Hq + h) * Spad + s;
-    if (s >= Sq) {
-      if (lane == 0) {
-        delta[stat] = 0.f;
-        lse2[stat] = INFINITY;
-      }
-      continue;
-    }
-    const size_t row_off = ((static_cast<size_t>(b) * Sq + s) * Hq + h) * D;
+    const bool real = in_range && s < Sq;
     float acc = 0.f;
-    for (int v = lane; v < vec_per_row; v += 32) {
-      const uint4 a = *reinterpret_cast<const uint4*>(out + row_off + v * 8);
-      const uint4 g = *reinterpret_cast<const uint4*>(dout + row_off + v * 8);
-      acc += dot8<T>(a, g);
+    if (real && gl < vec_per_row) {
+      const size_t row_off = ((static_cast<size_t>(b) * Sq + s) * Hq + h) * D;
+      const uint4 a = *reinterpret_cast<const uint4*>(out + row_off + gl * 8);
+      const uint4 g = *reinterpret_cast<const uint4*>(dout + row_off + gl * 8);
+      acc = dot8<T>(a, g);
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) {
-      delta[stat] = acc;
-      lse2[stat] = lse[stat] * 1.4426950408889634f;
+    for (int o = gsz >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (in_range && gl == 0) {
+      delta[stat] = real ? acc : 0.f;
+      lse2[stat] = real ? lse[stat] * 1.4426950408889634f : INFINITY;
     }
   }
 }
@@ -241,8 +243,9 @@ extern "C" int rfa_bwd_prepare(const void* out, const void* dout, const float* l
   const size_t dq_vec4 = static_cast<size_t>(B) * Hq * Spad * padded_head_dim(D) / 4;
   if (dq_acc && (reinterpret_cast<uintptr_t>(dq_acc) & 15u)) return RFA_ERR_INVALID_ARG;
   const int threads = 256;
-  long long blocks = (rows + 7) / 8;  // 8 warps per block, one row per warp per pass
-  if (blocks > 148ll * 32) blocks = 148ll * 32;
+  long long blocks = (rows + 15) / 16;  // 8 warps per block, at least two rows per warp pass
+  if (blocks > 148ll * 16) blocks = 148ll * 16;
+  if (blocks < 1) blocks = 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == RFA_DTYPE_BF16)
     bwd_prepare_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), threads, 0, s>>>(

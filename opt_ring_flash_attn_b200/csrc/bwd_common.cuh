@@ -1,0 +1,60 @@
+// Launch parameters of the backward hop kernel and the GQA-group split that fills the last wave of CTAs.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdlib.h>
+
+#include "common.h"
+
+namespace rfa {
+
+struct BwdParams {
+  const float* lse2;
+  const float* delta;
+  float* dq_acc;
+  const float* dkdv_prev;
+  float* dkdv_out;
+  int B, Sq, Skv, Hq, Hkv, D;
+  int Spad;
+  float scale, scale_log2;
+  int accumulate_prev, causal;
+  int gsplit;      // CTAs per (kv tile, kv head): each takes G / gsplit query heads of the group
+  int reduce_out;  // 1: the epilogue adds into dkdv_out with vector reductions (gsplit > 1); 0: plain stores
+  int* status;
+  unsigned long long* trace;
+  int trace_ctas, trace_cap;
+};
+
+// Work units are CTAs, one per SM at a time.  A grid that is not close to a multiple of 148 wastes the last
+// wave, so a GQA group may be split over several CTAs whose partial dK/dV are added with vector reductions.
+// Picks the smallest split that fills the waves to >= 90 % (override: RFA_B200_BWD_GSPLIT) and prepares
+// dkdv_out for the reducing epilogue (copy of the previous partial sums, or zeros).
+inline int choose_group_split(BwdParams& pr, long long base_units, cudaStream_t stream) {
+  const int G = pr.Hq / pr.Hkv;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int gsplit = 1; gsplit <= G; ++gsplit) {
+    if (G % gsplit) continue;
+    const long long units = base_units * gsplit;
+    const double eff = static_cast<double>(units) / static_cast<double>((units + 147) / 148 * 148);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = gsplit; }
+    if (eff >= 0.9) { best = gsplit; break; }
+  }
+  static const int forced = [] { const char* e = getenv("RFA_B200_BWD_GSPLIT"); return e ? atoi(e) : 0; }();
+  if (forced > 0 && G % forced == 0) best = forced;
+  pr.gsplit = best;
+  pr.reduce_out = best > 1 ? 1 : 0;
+  if (pr.reduce_out) {
+    const size_t bytes = static_cast<size_t>(2) * pr.B * pr.Skv * pr.Hkv * pr.D * sizeof(float);
+    cudaError_t e = cudaSuccess;
+    if (pr.accumulate_prev) {
+      if (pr.dkdv_prev != pr.dkdv_out) e = cudaMemcpyAsync(pr.dkdv_out, pr.dkdv_prev, bytes, cudaMemcpyDeviceToDevice, stream);
+    } else {
+      e = cudaMemsetAsync(pr.dkdv_out, 0, bytes, stream);
+    }
+    if (e != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
+  }
+  return RFA_OK;
+}
+
+}  // namespace rfa

@@ -25,27 +25,12 @@
 
 #include <type_traits>
 
+#include "bwd_common.cuh"
 #include "common.h"
 #include "tc05.cuh"
 
 namespace rfa {
 
-struct BwdParams {
-  const float* lse2;
-  const float* delta;
-  float* dq_acc;
-  const float* dkdv_prev;
-  float* dkdv_out;
-  int B, Sq, Skv, Hq, Hkv, D;
-  int Spad;
-  float scale, scale_log2;
-  int accumulate_prev, causal;
-  int gsplit;      // CTAs per (kv tile, kv head): each takes G / gsplit query heads of the group
-  int reduce_out;  // 1: the epilogue adds into dkdv_out with vector reductions (gsplit > 1); 0: plain stores
-  int* status;
-  unsigned long long* trace;
-  int trace_ctas, trace_cap;
-};
 
 template <int DP, int DH, int BQ, int NST>
 struct BwdCfg {
@@ -568,37 +553,11 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
     if (e != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
     attr_done = true;
   }
-  // Work units: one CTA per (kv tile, kv head, batch, head-dim half).  With 148 SMs and one CTA per SM a grid that is
-  // not close to a multiple of 148 wastes the last wave, so a GQA group may be split over several CTAs whose partial
-  // dK/dV are added with vector reductions.  Pick the smallest split that fills the waves to >= 90 %.
   BwdParams pr = prm;
-  const int G = prm.Hq / prm.Hkv;
   const long long base_units = static_cast<long long>(ceil_div(prm.Skv, 128)) * prm.Hkv * prm.B * Cfg::kHalves;
-  int best = 1;
-  double best_eff = 0.0;
-  for (int gsplit = 1; gsplit <= G; ++gsplit) {
-    if (G % gsplit) continue;
-    const long long units = base_units * gsplit;
-    const double eff = static_cast<double>(units) / static_cast<double>((units + 147) / 148 * 148);
-    if (eff > best_eff + 1e-9) { best_eff = eff; best = gsplit; }
-    if (eff >= 0.9) { best = gsplit; break; }
-  }
   {
-    // Tuning override (diagnostics): RFA_B200_BWD_GSPLIT=<divisor of the group size> forces the split.
-    static const int forced = [] { const char* e = getenv("RFA_B200_BWD_GSPLIT"); return e ? atoi(e) : 0; }();
-    if (forced > 0 && G % forced == 0) best = forced;
-  }
-  pr.gsplit = best;
-  pr.reduce_out = best > 1 ? 1 : 0;
-  if (pr.reduce_out) {
-    const size_t bytes = static_cast<size_t>(2) * prm.B * prm.Skv * prm.Hkv * prm.D * sizeof(float);
-    cudaError_t e = cudaSuccess;
-    if (prm.accumulate_prev) {
-      if (prm.dkdv_prev != prm.dkdv_out) e = cudaMemcpyAsync(prm.dkdv_out, prm.dkdv_prev, bytes, cudaMemcpyDeviceToDevice, stream);
-    } else {
-      e = cudaMemsetAsync(prm.dkdv_out, 0, bytes, stream);
-    }
-    if (e != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
+    const int rc2 = choose_group_split(pr, base_units, stream);
+    if (rc2 != RFA_OK) return rc2;
   }
   const unsigned grid = static_cast<unsigned>(base_units * pr.gsplit);
   kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, tdo, pr);
