@@ -76,6 +76,18 @@ int rfa_fwd_hop(const void* q, const void* k, const void* v, float* acc, float* 
                 int B, int Sq, int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale, int first, int last,
                 int causal_diag, int* status, void* stream);
 
+/*
+ * rfa_fwd_hop restricted to a window, for the zigzag layout (`_zigzag_forward`,
+ * optimized_ring_flash_attn.py:1140-1196): only query rows >= q_begin are processed (q_begin % 128 == 0), only
+ * keys < kv_len are visible, and query rows < q_split take `last_lo` where the others take `last` (in the
+ * zigzag schedule the front half of a rank's rows sees its final K/V block earlier than the back half).
+ * rfa_fwd_hop(...) == rfa_fwd_hop_window(..., q_begin=0, kv_len=Skv, q_split=0, last_lo=0).
+ */
+int rfa_fwd_hop_window(const void* q, const void* k, const void* v, float* acc, float* m, float* l, void* out,
+                       float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale,
+                       int first, int last, int causal_diag, int q_begin, int kv_len, int q_split, int last_lo,
+                       int* status, void* stream);
+
 /* Number of fp32 elements of the dQ accumulator (private tiled layout that makes the
  * per-tile reductions of the backward hop 16-byte vector operations; opaque to the caller). */
 size_t rfa_dq_acc_elems(int B, int Sq, int Hq, int D);
@@ -107,6 +119,17 @@ int rfa_bwd_hop(const void* q, const void* k, const void* v, const void* dout, c
                 float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B, int Sq, int Skv, int Hq, int Hkv,
                 int D, int dtype, float softmax_scale, int accumulate_prev, int causal_diag, int* status,
                 void* stream);
+
+/*
+ * rfa_bwd_hop restricted to a window, for the zigzag layout (`_zigzag_backward`,
+ * optimized_ring_flash_attn.py:1198-1275): only query rows >= q_begin contribute and only keys < kv_len are
+ * processed; rows of dkdv_out at or beyond kv_len receive the previous partial sums (accumulate_prev) or zero.
+ * rfa_bwd_hop(...) == rfa_bwd_hop_window(..., q_begin=0, kv_len=Skv).
+ */
+int rfa_bwd_hop_window(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
+                       const float* delta, float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B, int Sq,
+                       int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale, int accumulate_prev,
+                       int causal_diag, int q_begin, int kv_len, int* status, void* stream);
 
 /*
  * out[i] = prev[i] + block[i] for n fp32 elements (n % 4 == 0; out may alias prev or block).

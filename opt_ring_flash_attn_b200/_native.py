@@ -37,6 +37,8 @@ SIGNATURES = {
     "rfa_dq_acc_elems": (_sz, [_i, _i, _i, _i]),
     "rfa_bwd_dq_finalize": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "rfa_fwd_hop": (_i, [_vp] * 8 + [_i] * 7 + [_f] + [_i] * 3 + [_vp, _vp]),
+    "rfa_fwd_hop_window": (_i, [_vp] * 8 + [_i] * 7 + [_f] + [_i] * 7 + [_vp, _vp]),
+    "rfa_bwd_hop_window": (_i, [_vp] * 9 + [_i] * 7 + [_f] + [_i] * 4 + [_vp, _vp]),
     "rfa_bwd_prepare": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp]),
     "rfa_bwd_hop": (_i, [_vp] * 9 + [_i] * 7 + [_f] + [_i] * 2 + [_vp, _vp]),
     "rfa_noalloc_scratch_bytes": (_sz, []),
@@ -112,13 +114,16 @@ def fwd_acc_elems(B: int, Sq: int, Hq: int, D: int) -> int:
 
 
 def fwd_hop(q, k, v, acc, m, l, out, lse, softmax_scale: float, first: bool, last: bool, causal_diag: bool,
-            status: torch.Tensor, stream=None) -> None:
+            status: torch.Tensor, stream=None, q_begin: int = 0, kv_len: Optional[int] = None, q_split: int = 0,
+            last_lo: bool = False) -> None:
+    """One forward hop; the keyword arguments restrict it to a window (zigzag layout, see the C header)."""
     B, Sq, Hq, D = q.shape
     _, Skv, Hkv, _ = k.shape
-    rc = load().rfa_fwd_hop(
+    rc = load().rfa_fwd_hop_window(
         _ptr(q), _ptr(k), _ptr(v), _ptr(acc), _ptr(m), _ptr(l), _ptr(out), _ptr(lse),
         B, Sq, Skv, Hq, Hkv, D, DTYPE_CODES[q.dtype], float(softmax_scale),
-        int(first), int(last), int(causal_diag), _ptr(status), _stream(stream))
+        int(first), int(last), int(causal_diag), int(q_begin), int(Skv if kv_len is None else kv_len), int(q_split),
+        int(last_lo), _ptr(status), _stream(stream))
     _check(rc, "rfa_fwd_hop")
 
 
@@ -130,13 +135,15 @@ def bwd_prepare(out, dout, lse, delta, lse2, dq_acc, status, stream=None) -> Non
 
 
 def bwd_hop(q, k, v, dout, lse2, delta, dq_acc, dkdv_prev, dkdv_out, softmax_scale: float, accumulate_prev: bool,
-            causal_diag: bool, status, stream=None) -> None:
+            causal_diag: bool, status, stream=None, q_begin: int = 0, kv_len: Optional[int] = None) -> None:
+    """One backward hop; ``q_begin`` / ``kv_len`` restrict it to a window (zigzag layout, see the C header)."""
     B, Sq, Hq, D = q.shape
     _, Skv, Hkv, _ = k.shape
-    rc = load().rfa_bwd_hop(
+    rc = load().rfa_bwd_hop_window(
         _ptr(q), _ptr(k), _ptr(v), _ptr(dout), _ptr(lse2), _ptr(delta), _ptr(dq_acc), _ptr(dkdv_prev),
         _ptr(dkdv_out), B, Sq, Skv, Hq, Hkv, D, DTYPE_CODES[q.dtype], float(softmax_scale),
-        int(accumulate_prev), int(causal_diag), _ptr(status), _stream(stream))
+        int(accumulate_prev), int(causal_diag), int(q_begin), int(Skv if kv_len is None else kv_len),
+        _ptr(status), _stream(stream))
     _check(rc, "rfa_bwd_hop")
 
 

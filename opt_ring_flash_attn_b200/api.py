@@ -43,10 +43,13 @@ class _RingFlashAttnFunc(torch.autograd.Function):
             softmax_scale = q.shape[-1] ** -0.5
         if zigzag:
             assert causal, "zigzag mode requires causal=True"
-            raise NotImplementedError("zigzag layout is not available in this build")
         _validate(q, k, v, softmax_scale)
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        out, lse = schedule.ring_forward(group, q, k, v, softmax_scale, causal)
+        if zigzag:
+            out, lse = schedule.zigzag_forward(group, q, k, v, softmax_scale)
+        else:
+            out, lse = schedule.ring_forward(group, q, k, v, softmax_scale, causal)
+        ctx.zigzag = zigzag
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.softmax_scale = softmax_scale
         ctx.causal = causal
@@ -57,7 +60,10 @@ class _RingFlashAttnFunc(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout, _dlse=None):
         q, k, v, out, lse = ctx.saved_tensors
-        dq, dk, dv = schedule.ring_backward(ctx.group, dout, q, k, v, out, lse, ctx.softmax_scale, ctx.causal)
+        if ctx.zigzag:
+            dq, dk, dv = schedule.zigzag_backward(ctx.group, dout, q, k, v, out, lse, ctx.softmax_scale)
+        else:
+            dq, dk, dv = schedule.ring_backward(ctx.group, dout, q, k, v, out, lse, ctx.softmax_scale, ctx.causal)
         return dq, dk, dv, None, None, None, None
 
 
@@ -79,7 +85,9 @@ def ring_flash_attn(
       softmax_scale: 1/sqrt(D) by default.
       causal: causal mask over the full (global) sequence; rank r holds tokens
               [r*S_local, (r+1)*S_local).
-      zigzag: accepted for signature compatibility; raises NotImplementedError.
+      zigzag: causal load balancing: the global sequence is cut into 2W chunks and rank r holds
+              [chunk_r ; chunk_{2W-1-r}] concatenated along the sequence dim (requires causal=True and
+              S_local % 256 == 0).
       group:  process group (default: WORLD).  Without an initialised process
               group the call is plain single-GPU flash attention.
 
@@ -89,7 +97,8 @@ def ring_flash_attn(
     return out
 
 
-def ring_flash_attn_with_lse(q, k, v, softmax_scale=None, causal=False, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+def ring_flash_attn_with_lse(q, k, v, softmax_scale=None, causal=False, group=None,
+                             zigzag=False) -> Tuple[torch.Tensor, torch.Tensor]:
     """As :func:`ring_flash_attn`, also returning the log-sum-exp ``[B, H_q, S_local]`` (fp32, not differentiable)."""
-    out, lse = _RingFlashAttnFunc.apply(q, k, v, softmax_scale, causal, False, group)
+    out, lse = _RingFlashAttnFunc.apply(q, k, v, softmax_scale, causal, zigzag, group)
     return out, lse[:, :, : q.shape[1]]

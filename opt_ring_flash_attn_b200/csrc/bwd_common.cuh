@@ -18,6 +18,8 @@ struct BwdParams {
   int Spad;
   float scale, scale_log2;
   int accumulate_prev, causal;
+  int q_begin;  // window (zigzag layout): only query rows >= q_begin contribute
+  int kv_len;   // only keys < kv_len are processed; dK/dV rows beyond keep the previous partial sums (or zero)
   int gsplit;      // CTAs per (kv tile, kv head): each takes G / gsplit query heads of the group
   int reduce_out;  // 1: the epilogue adds into dkdv_out with vector reductions (gsplit > 1); 0: plain stores
   int* status;
@@ -44,7 +46,10 @@ inline int choose_group_split(BwdParams& pr, long long base_units, cudaStream_t 
   if (forced > 0 && G % forced == 0) best = forced;
   pr.gsplit = best;
   pr.reduce_out = best > 1 ? 1 : 0;
-  if (pr.reduce_out) {
+  // Rows of dkdv_out that the kernel does not write (keys beyond kv_len) must still hold prev (or zero): prepare the
+  // whole buffer in that case too.
+  const bool partial_rows = pr.kv_len < pr.Skv;
+  if (pr.reduce_out || (partial_rows && (!pr.accumulate_prev || pr.dkdv_prev != pr.dkdv_out))) {
     const size_t bytes = static_cast<size_t>(2) * pr.B * pr.Skv * pr.Hkv * pr.D * sizeof(float);
     cudaError_t e = cudaSuccess;
     if (pr.accumulate_prev) {

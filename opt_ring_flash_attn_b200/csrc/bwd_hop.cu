@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(512, 1)
   const int Gc = G / p.gsplit;
   const int n0 = kvt * 128;
   const int nQtiles = (p.Sq + BQ - 1) / BQ;
-  const int i_begin = p.causal ? (n0 / BQ) : 0;
+  const int i_begin = max(p.causal ? (n0 / BQ) : 0, p.q_begin / BQ);
   const int nI = nQtiles - i_begin;
   const int T_total = Gc * nI;
 
@@ -434,7 +434,7 @@ __global__ void __launch_bounds__(512, 1)
     if (ok) ok = mbar_wait_warp(&bar_final, 0, abort_p);
     if (ok) {
       tc_fence_after_sync();
-      const bool row_ok = kvpos < p.Skv;
+      const bool row_ok = kvpos < p.kv_len;
       const int which = (cw == 0) ? 1 : 0;  // packed buffer: [0] = dK, [1] = dV
       const float mul = (cw == 0) ? 1.0f : p.scale;
       const uint32_t a_acc = tmem_base + lane_addr + (cw == 0 ? Cfg::kTmDV : Cfg::kTmDK);
@@ -554,7 +554,7 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
     attr_done = true;
   }
   BwdParams pr = prm;
-  const long long base_units = static_cast<long long>(ceil_div(prm.Skv, 128)) * prm.Hkv * prm.B * Cfg::kHalves;
+  const long long base_units = static_cast<long long>(ceil_div(prm.kv_len, 128)) * prm.Hkv * prm.B * Cfg::kHalves;
   {
     const int rc2 = choose_group_split(pr, base_units, stream);
     if (rc2 != RFA_OK) return rc2;
@@ -577,16 +577,18 @@ static int dispatch_bwd(int dp, const void* q, const void* k, const void* v, con
 
 }  // namespace rfa
 
-extern "C" int rfa_bwd_hop(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
-                           const float* delta, float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B, int Sq,
-                           int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale, int accumulate_prev,
-                           int causal_diag, int* status, void* stream) {
+extern "C" int rfa_bwd_hop_window(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
+                                  const float* delta, float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B,
+                                  int Sq, int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale,
+                                  int accumulate_prev, int causal_diag, int q_begin, int kv_len, int* status,
+                                  void* stream) {
   using namespace rfa;
   if (!q || !k || !v || !dout || !lse2 || !delta || !dq_acc || !dkdv_out || !status) return RFA_ERR_INVALID_ARG;
   if (accumulate_prev && !dkdv_prev) return RFA_ERR_INVALID_ARG;
   if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0) return RFA_ERR_INVALID_ARG;
   if (!(softmax_scale > 0.f)) return RFA_ERR_INVALID_ARG;
   if (causal_diag && Sq != Skv) return RFA_ERR_INVALID_ARG;
+  if (q_begin < 0 || q_begin >= Sq || (q_begin % 128) != 0 || kv_len <= 0 || kv_len > Skv) return RFA_ERR_INVALID_ARG;
   const int dp = padded_head_dim(D);
   if (dp == 0) return RFA_ERR_UNSUPPORTED;
   if (dtype != RFA_DTYPE_BF16 && dtype != RFA_DTYPE_FP16) return RFA_ERR_UNSUPPORTED;
@@ -610,6 +612,8 @@ extern "C" int rfa_bwd_hop(const void* q, const void* k, const void* v, const vo
   prm.scale_log2 = softmax_scale * 1.4426950408889634f;
   prm.accumulate_prev = accumulate_prev ? 1 : 0;
   prm.causal = causal_diag ? 1 : 0;
+  prm.q_begin = q_begin;
+  prm.kv_len = kv_len;
   prm.gsplit = 1;
   prm.reduce_out = 0;
   prm.status = status;
@@ -619,4 +623,12 @@ extern "C" int rfa_bwd_hop(const void* q, const void* k, const void* v, const vo
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == RFA_DTYPE_BF16) return dispatch_bwd<__nv_bfloat16>(dp, q, k, v, dout, prm, dtype, s);
   return dispatch_bwd<__half>(dp, q, k, v, dout, prm, dtype, s);
+}
+
+extern "C" int rfa_bwd_hop(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
+                           const float* delta, float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B, int Sq,
+                           int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale, int accumulate_prev,
+                           int causal_diag, int* status, void* stream) {
+  return rfa_bwd_hop_window(q, k, v, dout, lse2, delta, dq_acc, dkdv_prev, dkdv_out, B, Sq, Skv, Hq, Hkv, D, dtype,
+                            softmax_scale, accumulate_prev, causal_diag, /*q_begin=*/0, /*kv_len=*/Skv, status, stream);
 }

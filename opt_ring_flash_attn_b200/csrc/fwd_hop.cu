@@ -32,6 +32,9 @@ struct FwdParams {
   int nQt;   // Spad / 128
   float scale_log2;
   int first, last, causal;
+  // Window (zigzag layout): only query rows >= q_begin are processed, only keys < kv_len are visible, and
+  // query rows < q_split take `last_lo` instead of `last` (their final hop can come earlier).
+  int q_begin, kv_len, q_split, last_lo;
   int* status;
   unsigned long long* trace;
   int trace_ctas, trace_cap;
@@ -103,7 +106,8 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
   const uint32_t s_kv = smem_base + NQ * Cfg::kQBytes;
 
   // ---- tile coordinates: heaviest (latest rows) first, heads fastest ----
-  const int nQs = (p.nQt + NQ - 1) / NQ;
+  const int tq0 = p.q_begin / 128;
+  const int nQs = (p.nQt - tq0 + NQ - 1) / NQ;
   const int per_qs = p.Hq * p.B;
   const int qs = nQs - 1 - static_cast<int>(blockIdx.x) / per_qs;
   const int rem = static_cast<int>(blockIdx.x) % per_qs;
@@ -111,12 +115,12 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
   const int h = rem % p.Hq;
   const int hkv = h / (p.Hq / p.Hkv);
 
-  const int nkv_total = (p.Skv + BN - 1) / BN;
+  const int nkv_total = (p.kv_len + BN - 1) / BN;
   int m0[NQ], ntile[NQ];
   int nmax = 0;
 #pragma unroll
   for (int q = 0; q < NQ; ++q) {
-    m0[q] = (qs * NQ + q) * 128;
+    m0[q] = (tq0 + qs * NQ + q) * 128;
     int n = 0;
     if (m0[q] < p.Sq) {
       n = nkv_total;
@@ -276,7 +280,8 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
     const int n = ntile[q];
     const int row_g = m0[q] + row;  // local query position
     const uint32_t o_addr = tmem_base + lane_addr + Cfg::kTmO + q * DP;
-    const int qt = qs * NQ + q;
+    const int qt = tq0 + qs * NQ + q;
+    const bool last_here = (m0[q] < p.q_split) ? (p.last_lo != 0) : (p.last != 0);
     const size_t bh = static_cast<size_t>(b) * p.Hq + h;
     float* acc_tile = p.acc + ((bh * p.nQt + qt) * (DP / 4)) * 512;  // [DP/4][128][4]
     const size_t ml_idx = bh * p.Spad + row_g;
@@ -304,7 +309,7 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
         tmem_st_wait();
       }
       // Highest visible local key index for this row.
-      const int col_lim = p.causal ? min(row_g, p.Skv - 1) : (p.Skv - 1);
+      const int col_lim = p.causal ? min(row_g, p.kv_len - 1) : (p.kv_len - 1);
 
 #pragma unroll 1
       for (int j = 0; j < n; ++j) {
@@ -316,7 +321,7 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
         tc_fence_after_sync();
         const uint32_t s_addr = tmem_base + lane_addr + Cfg::kTmS + (q * NS + sb) * BN;
         const int n0 = j * BN;
-        const bool masked = (p.causal && (n0 + BN - 1 > m0[q])) || (n0 + BN > p.Skv);
+        const bool masked = (p.causal && (n0 + BN - 1 > m0[q])) || (n0 + BN > p.kv_len);
 
         // The whole score row (BN fp32 values) goes to registers in one batch of loads.
         constexpr int NCH = BN / 32;
@@ -409,7 +414,7 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
       if (ok) ok = mbar_wait_warp(&bar_pv_done[q], (n - 1) & 1, abort_p);
       if (ok) {
         tc_fence_after_sync();
-        if (p.last) {
+        if (last_here) {
           const float inv = 1.0f / l_sum;
           const bool row_ok = row_g < p.Sq;
           T* orow = reinterpret_cast<T*>(p.out) + ((static_cast<size_t>(b) * p.Sq + row_g) * p.Hq + h) * p.D;
@@ -491,7 +496,7 @@ static int launch_fwd(const void* q, const void* k, const void* v, const FwdPara
     if (e != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
     attr_done = true;
   }
-  const int nQs = (prm.nQt + NQ - 1) / NQ;
+  const int nQs = (prm.nQt - prm.q_begin / 128 + NQ - 1) / NQ;
   const unsigned grid = static_cast<unsigned>(nQs) * prm.Hq * prm.B;
   kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, prm);
   return cuda_status(cudaGetLastError());
@@ -516,15 +521,21 @@ extern "C" size_t rfa_fwd_acc_elems(int B, int Sq, int Hq, int D) {
   return static_cast<size_t>(B) * Hq * rfa::round_up(Sq, 128) * dp;
 }
 
-extern "C" int rfa_fwd_hop(const void* q, const void* k, const void* v, float* acc, float* m, float* l, void* out,
-                           float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, int dtype,
-                           float softmax_scale, int first, int last, int causal_diag, int* status, void* stream) {
+extern "C" int rfa_fwd_hop_window(const void* q, const void* k, const void* v, float* acc, float* m, float* l,
+                                  void* out, float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, int dtype,
+                                  float softmax_scale, int first, int last, int causal_diag, int q_begin, int kv_len,
+                                  int q_split, int last_lo, int* status, void* stream) {
   using namespace rfa;
   if (!q || !k || !v || !status) return RFA_ERR_INVALID_ARG;
   if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0) return RFA_ERR_INVALID_ARG;
   if (!(softmax_scale > 0.f)) return RFA_ERR_INVALID_ARG;
-  if (!(first && last) && (!acc || !m || !l)) return RFA_ERR_INVALID_ARG;
-  if (last && (!out || !lse)) return RFA_ERR_INVALID_ARG;
+  if (q_begin < 0 || q_begin >= Sq || (q_begin % 128) != 0 || kv_len <= 0 || kv_len > Skv) return RFA_ERR_INVALID_ARG;
+  if (q_split < 0 || (q_split % 128) != 0) return RFA_ERR_INVALID_ARG;
+  const bool lo_exists = q_begin < q_split;
+  const bool hi_exists = q_split < Sq;
+  const bool all_final = first && (!hi_exists || last) && (!lo_exists || last_lo);
+  if (!all_final && (!acc || !m || !l)) return RFA_ERR_INVALID_ARG;
+  if (((hi_exists && last) || (lo_exists && last_lo)) && (!out || !lse)) return RFA_ERR_INVALID_ARG;
   if (causal_diag && Sq != Skv) return RFA_ERR_INVALID_ARG;
   const int dp = padded_head_dim(D);
   if (dp == 0) return RFA_ERR_UNSUPPORTED;
@@ -547,6 +558,10 @@ extern "C" int rfa_fwd_hop(const void* q, const void* k, const void* v, float* a
   prm.first = first ? 1 : 0;
   prm.last = last ? 1 : 0;
   prm.causal = causal_diag ? 1 : 0;
+  prm.q_begin = q_begin;
+  prm.kv_len = kv_len;
+  prm.q_split = q_split;
+  prm.last_lo = last_lo ? 1 : 0;
   prm.status = status;
   prm.trace = g_trace.buf;
   prm.trace_ctas = g_trace.ctas;
@@ -554,4 +569,11 @@ extern "C" int rfa_fwd_hop(const void* q, const void* k, const void* v, float* a
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == RFA_DTYPE_BF16) return dispatch_fwd<__nv_bfloat16>(dp, q, k, v, prm, dtype, s);
   return dispatch_fwd<__half>(dp, q, k, v, prm, dtype, s);
+}
+
+extern "C" int rfa_fwd_hop(const void* q, const void* k, const void* v, float* acc, float* m, float* l, void* out,
+                           float* lse, int B, int Sq, int Skv, int Hq, int Hkv, int D, int dtype,
+                           float softmax_scale, int first, int last, int causal_diag, int* status, void* stream) {
+  return rfa_fwd_hop_window(q, k, v, acc, m, l, out, lse, B, Sq, Skv, Hq, Hkv, D, dtype, softmax_scale, first, last,
+                            causal_diag, /*q_begin=*/0, /*kv_len=*/Skv, /*q_split=*/0, /*last_lo=*/0, status, stream);
 }

@@ -130,3 +130,106 @@ def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
     kn.cast_from_f32(final[0], dk)
     kn.cast_from_f32(final[1], dv)
     return dq, dk, dv
+
+
+def _zigzag_half(S: int) -> int:
+    # the kernels work on 128-row tiles: both halves of the local shard must be tile-aligned
+    if S % 256 != 0:
+        raise ValueError(f"zigzag needs S_local to be a multiple of 256, got {S}")
+    return S // 2
+
+
+def zigzag_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float, kernels=None):
+    """Causal ring forward over the zigzag layout: rank r holds ``[chunk_r ; chunk_{2W-1-r}]`` of 2W chunks.
+
+    Per-step rule of ``_zigzag_forward`` (optimized_ring_flash_attn.py:1130-1196): step 0 is causal attention on
+    the local shard; while ``step <= rank`` all local queries see the FRONT half of the visiting K/V block; after
+    that only the BACK half of the local queries sees the whole visiting block.  Every rank works on every step
+    (about half a block each), which is what balances the causal load.  The front half of the local rows is
+    final at ``step == rank`` (step 0 on rank 0), the back half at the last step.
+    """
+    kn = kernels if kernels is not None else _native
+    W, rank = _world(group)
+    B, S, Hq, D = q.shape
+    ws = workspace.forward_workspace(q, k, W)
+    out = torch.empty_like(q)
+    lse = torch.empty(B, Hq, _native.padded_seq(S), dtype=torch.float32, device=q.device)
+    if W == 1:
+        kn.fwd_hop(q, k, v, None, None, None, out, lse, softmax_scale, True, True, True, ws.status)
+        return out, lse
+    half = _zigzag_half(S)
+    comm = _transport(group, q.device, "fwd_kv")
+    kn.pack_kv(k, v, ws.kv_send)
+    cur = ws.kv_send
+    k_cur, v_cur = k, v
+    lo_final_step = rank  # rank 0: its front half only ever sees its own block
+    for step in range(W):
+        if step + 1 < W:
+            comm.post(cur, ws.kv_recv[step & 1])
+        last_hi = step == W - 1
+        last_lo = step == lo_final_step
+        if step == 0:
+            kn.fwd_hop(q, k_cur, v_cur, ws.acc, ws.m, ws.l, out, lse, softmax_scale, True, last_hi, True, ws.status,
+                       q_begin=0, kv_len=S, q_split=half, last_lo=last_lo)
+        elif step <= rank:
+            kn.fwd_hop(q, k_cur, v_cur, ws.acc, ws.m, ws.l, out, lse, softmax_scale, False, last_hi, False,
+                       ws.status, q_begin=0, kv_len=half, q_split=half, last_lo=last_lo)
+        else:
+            kn.fwd_hop(q, k_cur, v_cur, ws.acc, ws.m, ws.l, out, lse, softmax_scale, False, last_hi, False,
+                       ws.status, q_begin=half, kv_len=S, q_split=half, last_lo=False)
+        if step + 1 < W:
+            comm.wait()
+            cur = ws.kv_recv[step & 1]
+            k_cur, v_cur = cur[0], cur[1]
+    return out, lse
+
+
+def zigzag_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                    lse: torch.Tensor, softmax_scale: float, kernels=None):
+    """Backward of :func:`zigzag_forward`; same window rule per step (optimized_ring_flash_attn.py:1198-1275),
+    same two rings and slot algebra as :func:`ring_backward`."""
+    kn = kernels if kernels is not None else _native
+    W, rank = _world(group)
+    if W == 1:
+        return ring_backward(group, dout, q, k, v, out, lse, softmax_scale, True, kernels=kernels)
+    S = q.shape[1]
+    half = _zigzag_half(S)
+    ws = workspace.backward_workspace(q, k, W)
+    dout = dout.contiguous()
+    kn.bwd_prepare(out, dout, lse, ws.delta, ws.lse2, ws.dq_acc, ws.status)
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+    kv_comm = _transport(group, q.device, "bwd_kv")
+    dkv_comm = _transport(group, q.device, "bwd_dkdv")
+    kn.pack_kv(k, v, ws.kv_send)
+    cur = ws.kv_send
+    k_cur, v_cur = k, v
+    for step in range(W):
+        if step + 1 < W:
+            kv_comm.post(cur, ws.kv_recv[step & 1])
+        prev_slot = (step - 1) & 1
+        buf = ws.dkdv[prev_slot]
+        if step == 0:
+            kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, buf, softmax_scale, False, True,
+                       ws.status, q_begin=0, kv_len=S)
+        elif step <= rank:
+            kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, ws.block_dkdv, softmax_scale, False,
+                       False, ws.status, q_begin=0, kv_len=half)
+        else:
+            kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, ws.block_dkdv, softmax_scale, False,
+                       False, ws.status, q_begin=half, kv_len=S)
+        if step > 0:
+            dkv_comm.wait()
+            kn.dkdv_accumulate(buf, ws.block_dkdv, buf)
+        if step + 1 < W:
+            kv_comm.wait()
+            cur = ws.kv_recv[step & 1]
+            k_cur, v_cur = cur[0], cur[1]
+        dkv_comm.post(buf, ws.dkdv[step & 1])
+    dkv_comm.wait()
+    final = ws.dkdv[(W - 1) & 1]
+    kn.dq_finalize(ws.dq_acc, dq)
+    kn.cast_from_f32(final[0], dk)
+    kn.cast_from_f32(final[1], dv)
+    return dq, dk, dv

@@ -193,6 +193,28 @@ def shard(x: torch.Tensor, world_size: int) -> List[torch.Tensor]:
     return [c.contiguous() for c in x.chunk(world_size, dim=1)]
 
 
+def zigzag_shard(x: torch.Tensor, world_size: int) -> List[torch.Tensor]:
+    """Zigzag layout of the reference (optimized_ring_flash_attn.py:1122-1124): the sequence is cut into 2W chunks
+    and rank r holds ``[chunk_r ; chunk_{2W-1-r}]``."""
+    c = x.chunk(2 * world_size, dim=1)
+    return [torch.cat([c[r], c[2 * world_size - 1 - r]], dim=1).contiguous() for r in range(world_size)]
+
+
+def zigzag_oracle(q, k, v, dout, world_size: int, softmax_scale: Optional[float] = None,
+                  compute_dtype: torch.dtype = torch.float32, head_chunk: int = 0) -> Dict[str, List[torch.Tensor]]:
+    """Expected per-rank results of causal attention in the zigzag layout: the pinned contiguous-shard oracle is
+    run over 2W chunks of the full sequence and its per-chunk results are regrouped rank by rank."""
+    W2 = 2 * world_size
+    res = ring_attn_oracle(shard(q, W2), shard(k, W2), shard(v, W2), shard(dout, W2) if dout is not None else None,
+                           causal=True, softmax_scale=softmax_scale, compute_dtype=compute_dtype,
+                           head_chunk=head_chunk)
+    out: Dict[str, List[torch.Tensor]] = {}
+    for key, parts in res.items():
+        dim = 2 if key == "lse" else 1
+        out[key] = [torch.cat([parts[r], parts[W2 - 1 - r]], dim=dim) for r in range(world_size)]
+    return out
+
+
 def make_inputs(seed: int, B: int, S_total: int, Hq: int, Hkv: int, D: int, std: float = 1.0,
                 dtype: torch.dtype = torch.float32):
     """Seeded full-sequence q, k, v, dout drawn in that order on the CPU generator

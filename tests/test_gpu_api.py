@@ -53,8 +53,6 @@ def test_argument_errors():
 
     dev = torch.device("cuda:0")
     q = torch.zeros(1, 128, 4, 64, dtype=torch.bfloat16, device=dev)
-    with pytest.raises(NotImplementedError):
-        ring_flash_attn(q, q, q, causal=True, zigzag=True)
     with pytest.raises(AssertionError):
         ring_flash_attn(q, q, q, causal=False, zigzag=True)
     with pytest.raises(AssertionError):
@@ -63,6 +61,15 @@ def test_argument_errors():
         ring_flash_attn(q.float(), q.float(), q.float())
     with pytest.raises(ValueError):
         ring_flash_attn(q[..., :60], q[..., :60], q[..., :60])
+
+
+def test_zigzag_flag_single_gpu_equals_causal():
+    """With one rank the zigzag layout is the plain sequence: zigzag=True must equal causal=True."""
+    from opt_ring_flash_attn_b200 import ring_flash_attn
+
+    dev = torch.device("cuda:0")
+    q, k, v, _ = (x.to(dev) for x in make_inputs(34, 1, 256, 2, 2, 64, dtype=torch.bfloat16))
+    assert torch.equal(ring_flash_attn(q, k, v, causal=True, zigzag=True), ring_flash_attn(q, k, v, causal=True))
 
 
 def test_non_contiguous_inputs():
@@ -75,3 +82,24 @@ def test_non_contiguous_inputs():
     o1 = ring_flash_attn(q, k, v)
     o2 = ring_flash_attn(qt, k, v)
     assert torch.equal(o1, o2)
+
+
+def test_baseline_style_wrappers():
+    """The zhuzilin-style entry points give the operator's results (packed inputs are strided views)."""
+    import opt_ring_flash_attn_b200 as rfa
+
+    dev = torch.device("cuda:0")
+    q, k, v, dout = (x.to(dev) for x in make_inputs(35, 1, 256, 4, 4, 64, dtype=torch.bfloat16))
+    base = rfa.ring_flash_attn(q, k, v, causal=True)
+    assert torch.equal(rfa.ring_flash_attn_func(q, k, v, causal=True), base)
+    kv = torch.stack([k, v], dim=2)
+    assert torch.equal(rfa.ring_flash_attn_kvpacked_func(q, kv, causal=True), base)
+    qkv = torch.stack([q, k, v], dim=2).requires_grad_(True)
+    out, lse, probs = rfa.ring_flash_attn_qkvpacked_func(qkv, causal=True, return_attn_probs=True)
+    assert probs is None and lse.shape == (1, 4, 256) and torch.equal(out, base)
+    out.backward(dout)
+    assert qkv.grad is not None and torch.isfinite(qkv.grad.float()).all()
+    with pytest.raises(NotImplementedError):
+        rfa.ring_flash_attn_func(q, k, v, dropout_p=0.1)
+    with pytest.raises(NotImplementedError):
+        rfa.ring_flash_attn_func(q, k, v, window_size=(128, 0))

@@ -28,18 +28,27 @@ def _worker(rank, world, port, cfg, errs):
         from opt_ring_flash_attn_b200 import _native, ring_flash_attn_with_lse, workspace
         from oracle.ring_attn_oracle import make_inputs, ring_attn_oracle, shard
 
-        B, S, Hq, Hkv, D, causal, dtype = cfg
+        from oracle.ring_attn_oracle import zigzag_oracle, zigzag_shard
+
+        B, S, Hq, Hkv, D, causal, dtype = cfg[:7]
+        zigzag = len(cfg) > 7 and cfg[7]
         q, k, v, dout = (x.to(dev) for x in make_inputs(60, B, S * world, Hq, Hkv, D, dtype=dtype))
-        qs, ks, vs, dos = shard(q, world), shard(k, world), shard(v, world), shard(dout, world)
+        if zigzag:
+            qs, ks, vs, dos = (zigzag_shard(x, world) for x in (q, k, v, dout))
+        else:
+            qs, ks, vs, dos = shard(q, world), shard(k, world), shard(v, world), shard(dout, world)
         ql, kl, vl = (x[rank].clone().requires_grad_(True) for x in (qs, ks, vs))
         for it in range(2):  # second iteration reuses the cached workspaces and transports
             ql.grad = kl.grad = vl.grad = None
-            out, lse = ring_flash_attn_with_lse(ql, kl, vl, causal=causal, group=dist.group.WORLD)
+            out, lse = ring_flash_attn_with_lse(ql, kl, vl, causal=causal, group=dist.group.WORLD, zigzag=zigzag)
             out.backward(dos[rank])
         torch.cuda.synchronize()
         for ws in list(workspace._fwd_cache.values()) + list(workspace._bwd_cache.values()):
             _native.check_status(ws.status, "ring")
-        ref = ring_attn_oracle(qs, ks, vs, dos, causal=causal, head_chunk=4)
+        if zigzag:
+            ref = zigzag_oracle(q, k, v, dout, world, head_chunk=4)
+        else:
+            ref = ring_attn_oracle(qs, ks, vs, dos, causal=causal, head_chunk=4)
 
         def rel(a, b):
             return ((a.float() - b).norm() / b.norm()).item()
@@ -62,6 +71,7 @@ def _worker(rank, world, port, cfg, errs):
     (1, 384, 8, 2, 128, False, torch.bfloat16),
     (2, 256, 4, 2, 64, True, torch.float16),
     (1, 320, 2, 2, 256, True, torch.bfloat16),
+    (1, 512, 4, 2, 128, True, torch.bfloat16, True),  # zigzag layout
 ])
 def test_ring_nccl(cfg):
     import torch.multiprocessing as mp

@@ -53,6 +53,24 @@ def test_oracle_matches_dense_attention(W, causal, Hq, Hkv):
     assert torch.allclose(_cat(res["dv"]), v.grad, atol=2e-5)
 
 
+def test_zigzag_oracle_matches_dense_attention():
+    from oracle.ring_attn_oracle import zigzag_oracle, zigzag_shard
+
+    W, B, S_total, Hq, Hkv, D = 3, 1, 192, 4, 2, 16
+    q, k, v, dout = make_inputs(12, B, S_total, Hq, Hkv, D)
+    q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    out_d, lse_d = dense_attention(q, k, v, True)
+    out_d.backward(dout)
+    res = zigzag_oracle(q.detach(), k.detach(), v.detach(), dout, W)
+    for key, full in (("out", out_d.detach()), ("dq", q.grad), ("dk", k.grad), ("dv", v.grad)):
+        want = zigzag_shard(full, W)
+        for r in range(W):
+            assert torch.allclose(res[key][r], want[r], atol=2e-5), key
+    want = zigzag_shard(lse_d.detach().transpose(1, 2), W)
+    for r in range(W):
+        assert torch.allclose(res["lse"][r].transpose(1, 2), want[r], atol=2e-5)
+
+
 def test_merge_identity():
     """Online-softmax merge identity of the reference's merge kernel (optimized_ring_flash_attn.py:377-383):
     merging two blocks by their LSEs equals attention over their union."""

@@ -89,6 +89,63 @@ def test_ring_schedules_on_gloo(world, causal, Hq, Hkv, sub):
     assert not msgs and all(p.exitcode == 0 for p in procs), msgs
 
 
+def _zz_worker(rank, world, port, Hq, Hkv, errs):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    try:
+        import sys
+        sys.path.insert(0, os.path.dirname(__file__))
+        import fake_kernels
+        from opt_ring_flash_attn_b200 import schedule
+        from oracle.ring_attn_oracle import zigzag_oracle, zigzag_shard
+
+        B, S, D = 1, 256, 16  # S_local = 256: two 128-row halves
+        q, k, v, dout = make_inputs(70, B, S * world, Hq, Hkv, D, dtype=torch.bfloat16)
+        qs, ks, vs, dos = (zigzag_shard(x, world) for x in (q, k, v, dout))
+        scale = 0.25
+        out, lse = schedule.zigzag_forward(None, qs[rank], ks[rank], vs[rank], scale, kernels=fake_kernels)
+        dq, dk, dv = schedule.zigzag_backward(None, dos[rank], qs[rank], ks[rank], vs[rank], out, lse, scale,
+                                              kernels=fake_kernels)
+        ref = zigzag_oracle(q, k, v, dout, world, softmax_scale=scale)
+
+        def rel(a, b):
+            return ((a.float() - b).norm() / b.norm()).item()
+
+        assert (out.float() - ref["out"][rank]).abs().max().item() <= 1e-2
+        assert (lse[:, :, :S] - ref["lse"][rank]).abs().max().item() <= 1e-3
+        assert rel(dq, ref["dq"][rank]) <= 2e-2, rel(dq, ref["dq"][rank])
+        assert rel(dk, ref["dk"][rank]) <= 2e-2, rel(dk, ref["dk"][rank])
+        assert rel(dv, ref["dv"][rank]) <= 2e-2, rel(dv, ref["dv"][rank])
+        dist.barrier()
+    except Exception as e:
+        errs.put(f"rank {rank}: {type(e).__name__}: {e}")
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,Hq,Hkv", [(2, 2, 2), (3, 4, 2)])
+def test_zigzag_schedules_on_gloo(world, Hq, Hkv):
+    ctx = mp.get_context("spawn")
+    errs = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_zz_worker, args=(r, world, port, Hq, Hkv, errs)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+    msgs = []
+    while not errs.empty():
+        msgs.append(errs.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            msgs.append("a rank did not finish in time")
+    assert not msgs and all(p.exitcode == 0 for p in procs), msgs
+
+
 def test_transport_rejects_same_buffer_and_unposted_wait():
     """Error behaviour of the transport mirrors the reference's comm helpers (RuntimeError on misuse)."""
     port = _free_port()
