@@ -217,6 +217,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--zigzag", action="store_true",
+                    help="zigzag layout (rank r holds chunks r and 2W-1-r): balanced causal work; not the headline config")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     B, S, Hq, Hkv, D, scale, std, seed, desc = cfg
@@ -247,7 +249,7 @@ def main():
 
     def step_device():
         qg.grad = kg.grad = vg.grad = None
-        out = ring_flash_attn(qg, kg, vg, softmax_scale=scale, causal=True)
+        out = ring_flash_attn(qg, kg, vg, softmax_scale=scale, causal=True, zigzag=args.zigzag)
         out.backward(dout)
         return out
 
@@ -345,7 +347,7 @@ def main():
             dv_.copy_(hv, non_blocking=True)
             ddo_.copy_(hdo, non_blocking=True)
             a, b_, c = (x.detach().requires_grad_(True) for x in (dq_, dk_, dv_))
-            o = ring_flash_attn(a, b_, c, softmax_scale=scale, causal=True)
+            o = ring_flash_attn(a, b_, c, softmax_scale=scale, causal=True, zigzag=args.zigzag)
             o.backward(ddo_)
             h_out.copy_(o.detach(), non_blocking=True)
             h_dq.copy_(a.grad, non_blocking=True)
@@ -375,7 +377,8 @@ def main():
         W = world
         fb = f_blk(B, S, Hq, D)
         flops_job = 3.5 * (W * W / 2.0) * fb
-        flops_slowest = 3.5 * (W - 0.5) * fb
+        # contiguous shards: the last rank does W - 1/2 block-equivalents; zigzag: every rank does W/2
+        flops_slowest = 3.5 * (W / 2.0 if args.zigzag else (W - 0.5)) * fb
         value = flops_job / (ms_max * 1e-3) / 1e12
         slowest = flops_slowest / (ms_max * 1e-3) / 1e12
         peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
@@ -387,7 +390,8 @@ def main():
             "metric": "causal_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": W, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.config}: {desc}, causal, fwd+bwd, world size {W}",
+            "config": {"workload": f"{args.config}: {desc}, causal, fwd+bwd, world size {W}"
+                                   + (", zigzag layout" if args.zigzag else ", contiguous shards"),
                        "l2": "L2 flushed (256 MiB write) between timed steps" if flush is not None
                              else "per-step inputs+outputs exceed the 126 MB L2",
                        "flops": "algorithmic causal FLOPs: 3.5*(W^2/2)*4*B*Hq*S_local^2*D for the job"},
