@@ -40,6 +40,7 @@ extern "C" {
 #define RFA_ERR_UNSUPPORTED (-2) /* head dim not a multiple of 8 or above 256, unknown dtype */
 #define RFA_ERR_CUDA (-3)        /* a CUDA runtime call or the launch failed */
 #define RFA_ERR_DRIVER (-4)      /* the driver rejected a tensor-map descriptor */
+#define RFA_ERR_NCCL (-6)        /* NCCL is not loadable or an NCCL call failed */
 #define RFA_ERR_TOO_LARGE (-5)   /* the shape needs more scratch than rfa_bwd_hop_noalloc's fixed array holds */
 
 #define RFA_DTYPE_BF16 0
@@ -183,6 +184,27 @@ int rfa_cast_from_f32(const float* src, void* dst, size_t n, int dtype, void* st
  * kv_send[1].copy_(v)` (optimized_ring_flash_attn.py:836-838, 974-976).
  */
 int rfa_pack_kv(const void* k, const void* v, void* dst, size_t bytes_each, void* stream);
+
+/*
+ * Ring transport on a private NCCL communicator (the transfers of `DoubleBufRingComm`,
+ * optimized_ring_flash_attn.py:163-188, without a Python process-group round trip per hop).
+ *
+ *  rfa_comm_unique_id(out128)   rank 0 of the ring: fills 128 bytes of host memory to be sent to every rank
+ *  rfa_comm_init(id, rank, W, &handle)   collective over the W ranks of the ring (W >= 2), current device;
+ *                               the handle owns the communicator, one stream and a few events
+ *  rfa_ring_post(handle, send, recv, bytes, compute_stream)
+ *        after everything already enqueued on compute_stream: send `bytes` from `send` to rank+1 and receive
+ *        `bytes` into `recv` from rank-1, as one NCCL group on the handle's own stream.  Returns a slot >= 0
+ *        (or a negative error).  Asynchronous.  send and recv must differ.
+ *  rfa_ring_wait(handle, slot, compute_stream)   compute_stream waits for that transfer; the host does not.
+ *  rfa_comm_destroy(handle)
+ * At most 8 posts may be outstanding (not yet waited for) per handle.  Host pointers: out128, id, handle.
+ */
+int rfa_comm_unique_id(void* out128);
+int rfa_comm_init(const void* id128, int rank, int world, void** handle);
+int rfa_comm_destroy(void* handle);
+int rfa_ring_post(void* handle, const void* send, void* recv, size_t bytes, void* compute_stream);
+int rfa_ring_wait(void* handle, int slot, void* compute_stream);
 
 /*
  * Diagnostic: one 128x128x128 tensor-core product through each operand path the

@@ -23,6 +23,7 @@ ERROR_NAMES = {
     -3: "RFA_ERR_CUDA",
     -4: "RFA_ERR_DRIVER",
     -5: "RFA_ERR_TOO_LARGE",
+    -6: "RFA_ERR_NCCL",
 }
 STATUS_NAMES = {0: "ok", 1: "a bounded pipeline wait inside a kernel ran out of time"}
 
@@ -46,6 +47,11 @@ SIGNATURES = {
     "rfa_dkdv_accumulate": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "rfa_cast_from_f32": (_i, [_vp, _vp, _sz, _i, _vp]),
     "rfa_pack_kv": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "rfa_comm_unique_id": (_i, [_vp]),
+    "rfa_comm_init": (_i, [_vp, _i, _i, ctypes.POINTER(ctypes.c_void_p)]),
+    "rfa_comm_destroy": (_i, [_vp]),
+    "rfa_ring_post": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "rfa_ring_wait": (_i, [_vp, _i, _vp]),
     "rfa_debug_mma_probe": (_i, [_i, _vp, _vp, _vp, _vp, _vp]),
     "rfa_debug_set_trace": (_i, [_vp, _i, _i]),
 }
@@ -195,6 +201,35 @@ def pack_kv(k: torch.Tensor, v: torch.Tensor, dst: torch.Tensor, stream=None) ->
 def mma_probe(mode: int, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, status: torch.Tensor, stream=None) -> None:
     rc = load().rfa_debug_mma_probe(mode, _ptr(a), _ptr(b), _ptr(c), _ptr(status), _stream(stream))
     _check(rc, "rfa_debug_mma_probe")
+
+
+def comm_unique_id() -> bytes:
+    buf = ctypes.create_string_buffer(128)
+    _check(load().rfa_comm_unique_id(buf), "rfa_comm_unique_id", kernels=0)
+    return buf.raw
+
+
+def comm_init(unique_id: bytes, rank: int, world: int) -> int:
+    handle = ctypes.c_void_p()
+    _check(load().rfa_comm_init(ctypes.c_char_p(unique_id), rank, world, ctypes.byref(handle)), "rfa_comm_init",
+           kernels=0)
+    return handle.value
+
+
+def comm_destroy(handle: int) -> None:
+    _check(load().rfa_comm_destroy(handle), "rfa_comm_destroy", kernels=0)
+
+
+def ring_post(handle: int, send: torch.Tensor, recv: torch.Tensor, stream=None) -> int:
+    nbytes = send.numel() * send.element_size()
+    slot = load().rfa_ring_post(handle, _ptr(send), _ptr(recv), nbytes, _stream(stream))
+    if slot < 0:
+        _check(slot, "rfa_ring_post", kernels=0)
+    return slot
+
+
+def ring_wait(handle: int, slot: int, stream=None) -> None:
+    _check(load().rfa_ring_wait(handle, slot, _stream(stream)), "rfa_ring_wait", kernels=0)
 
 
 def set_trace(buf: Optional[torch.Tensor], n_ctas: int = 0, cap: int = 0) -> None:

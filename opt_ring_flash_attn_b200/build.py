@@ -21,7 +21,7 @@ LIB_NAME = "librfa_b200.so"
 LIB_PATH = PKG_DIR / LIB_NAME
 OBJ_DIR = PKG_DIR / "build"
 
-SOURCES = ["aux.cu", "fwd_hop.cu", "bwd_hop.cu", "probe.cu", "noalloc.cu"]
+SOURCES = ["aux.cu", "fwd_hop.cu", "bwd_hop.cu", "probe.cu", "noalloc.cu", "comm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
@@ -71,7 +71,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as ex:
         objs = list(ex.map(compile_one, SOURCES))
-    link = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
+    link = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a", "-ldl"]
     res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)

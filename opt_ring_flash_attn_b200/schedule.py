@@ -24,18 +24,18 @@ import torch
 import torch.distributed as dist
 
 from . import _native, workspace
-from .transport import RingTransport
+from .transport import make_transport
 
 
 _transports = {}
 
 
-def _transport(group, device: torch.device, tag: str) -> RingTransport:
+def _transport(group, device: torch.device, tag: str):
     """One transport (and side stream) per (group, device, ring) for the life of the process."""
     key = (id(group) if group is not None else None, str(device), tag)
     t = _transports.get(key)
     if t is None or t.world_size != dist.get_world_size(group):
-        t = RingTransport(group, device)
+        t = make_transport(group, device)
         _transports[key] = t
     return t
 
