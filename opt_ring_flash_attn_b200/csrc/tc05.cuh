@@ -353,9 +353,6 @@ __device__ __forceinline__ void tmem_ld_wait32(uint32_t (&r)[32]) {
 __device__ __forceinline__ void reg_fence32(uint32_t (&r)[32]) {
   asm volatile("" : RFA_RW8(r, 0), RFA_RW8(r, 8), RFA_RW8(r, 16), RFA_RW8(r, 24) : : "memory");
 }
-__device__ __forceinline__ void red_add_f32(float* gptr, float v) {
-  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(gptr), "f"(v) : "memory");
-}
 // 16-byte vector reduction (sm_90+): four consecutive floats, one L2 operation.
 __device__ __forceinline__ void red_add_v4_f32(float* gptr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gptr), "f"(a), "f"(b), "f"(c), "f"(d)
