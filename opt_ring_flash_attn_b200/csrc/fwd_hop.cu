@@ -8,8 +8,8 @@
 // Structure of one CTA (sm_100a):
 //   warp 0      TMA producer: Q tile(s) once, then K_j / V_j tiles through a ring
 //               of shared-memory slots guarded by full/empty mbarriers.
-//   warp 1      MMA issuer (one thread): S = Q K_j^T  (tcgen05.mma, operands in
-//               shared memory) and O += P_j V_j (P read from tensor memory).
+//   warp 1      MMA issuer (loop run by the whole warp, one elected lane issues): S = Q K_j^T
+//               (tcgen05.mma, operands in shared memory) and O += P_j V_j (P read from tensor memory).
 //   warps 4..   one softmax warpgroup per Q tile: thread = query row = TMEM lane;
 //               reads S from tensor memory, exp2-domain online softmax with lazy
 //               rescaling of O, writes P (16-bit) back over S.
@@ -58,22 +58,23 @@ struct FwdCfg {
 
 // S[128 x BN] = Q[128 x DP] * K[BN x DP]^T, both operands K-major.
 template <int DP, int BN>
-__device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_smem, uint32_t k_smem, uint32_t idesc) {
+__device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_smem, uint32_t k_smem, uint32_t idesc,
+                                         uint32_t el) {
   // q_smem / k_smem are descriptor low words of the tile bases; offsets are in 16-byte units
   static_for<0, DP / 16>([&](auto ks_) {
     constexpr int ks = decltype(ks_)::value;
-    mma_ss_off<(((ks / 4) * (128 * 128) + (ks % 4) * 32) / 16), (((ks / 4) * (BN * 128) + (ks % 4) * 32) / 16)>(
-        s_tmem, q_smem, k_smem, idesc, ks > 0 ? 1u : 0u);
+    mma_ss_off_e<(((ks / 4) * (128 * 128) + (ks % 4) * 32) / 16), (((ks / 4) * (BN * 128) + (ks % 4) * 32) / 16)>(
+        s_tmem, q_smem, k_smem, idesc, ks > 0 ? 1u : 0u, el);
   });
 }
 
 // O[128 x DP] (+)= P[128 x BN] * V[BN x DP]; P in tensor memory, V MN-major.
 template <int DP, int BN>
 __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint32_t v_smem, uint32_t idesc,
-                                         bool accumulate) {
+                                         bool accumulate, uint32_t el) {
   static_for<0, BN / 16>([&](auto ks_) {
     constexpr int ks = decltype(ks_)::value;
-    mma_ts_off<(ks * 8), (ks * 128)>(o_tmem, p_tmem, v_smem, idesc, (accumulate || ks > 0) ? 1u : 0u);
+    mma_ts_off_e<(ks * 8), (ks * 128)>(o_tmem, p_tmem, v_smem, idesc, (accumulate || ks > 0) ? 1u : 0u, el);
   });
 }
 
@@ -202,7 +203,11 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
     __syncwarp();
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
-    if (lane == 0) {
+    // The whole warp runs this loop converged; the elected lane issues.  A commit makes its mbarrier track every MMA
+    // issued before it, so the arrival on bar_s_full for tile j+1 also tells the softmax warps that O += P_j V_j has
+    // retired; bar_pv_done is only needed after the last tile.
+    {
+      const uint32_t el = elect_one();
       constexpr uint32_t idesc_qk = make_idesc(128, BN, kBf16, false, false);
       constexpr uint32_t idesc_pv = make_idesc(128, DP, kBf16, false, true);
       auto slot_of = [&](int u) { return u % kSlots; };
@@ -216,58 +221,58 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
       auto s_tm = [&](int q, int sb) { return tmem_base + Cfg::kTmS + (q * NS + sb) * BN; };
       auto o_tm = [&](int q) { return tmem_base + Cfg::kTmO + q * DP; };
       bool ok = nmax > 0;
-      if (ok) ok = mbar_wait(&bar_q_full, 0, abort_p);
-      if (ok) ok = mbar_wait(&bar_kv_full[slot_of(0)], par_of(0), abort_p);
+      if (ok) ok = mbar_wait_warp(&bar_q_full, 0, abort_p);
+      if (ok) ok = mbar_wait_warp(&bar_kv_full[slot_of(0)], par_of(0), abort_p);
       if (ok) {
         tc_fence_after_sync();
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
           if (ntile[q] > 0) {
-            issue_qk<DP, BN>(s_tm(q, 0), q_lo[q], k_lo(0), idesc_qk);
-            mma_commit(&bar_s_full[q * NS + 0]);
+            issue_qk<DP, BN>(s_tm(q, 0), q_lo[q], k_lo(0), idesc_qk, el);
+            mma_commit_e(&bar_s_full[q * NS + 0], el);
           }
         }
-        mma_commit(&bar_kv_empty[slot_of(0)]);
+        mma_commit_e(&bar_kv_empty[slot_of(0)], el);
       }
       for (int j = 0; j < nmax && ok; ++j) {
         if (NS == 2) {
           // Score buffer (j+1)&1 is free: P_{j-1} was consumed by the PV issued last iteration.
           if (j + 1 < ntile[0]) {
             const int uk = 2 * (j + 1);
-            if (!mbar_wait(&bar_kv_full[slot_of(uk)], par_of(uk), abort_p)) { ok = false; break; }
+            if (!mbar_wait_warp(&bar_kv_full[slot_of(uk)], par_of(uk), abort_p)) { ok = false; break; }
             tc_fence_after_sync();
-            issue_qk<DP, BN>(s_tm(0, (j + 1) & 1), q_lo[0], k_lo(uk), idesc_qk);
-            mma_commit(&bar_s_full[(j + 1) & 1]);
-            mma_commit(&bar_kv_empty[slot_of(uk)]);
+            issue_qk<DP, BN>(s_tm(0, (j + 1) & 1), q_lo[0], k_lo(uk), idesc_qk, el);
+            mma_commit_e(&bar_s_full[(j + 1) & 1], el);
+            mma_commit_e(&bar_kv_empty[slot_of(uk)], el);
           }
         }
         const int uv = 2 * j + 1;
         tr.mark(9);
-        if (!mbar_wait(&bar_kv_full[slot_of(uv)], par_of(uv), abort_p)) { ok = false; break; }
+        if (!mbar_wait_warp(&bar_kv_full[slot_of(uv)], par_of(uv), abort_p)) { ok = false; break; }
         tr.mark(10);
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
           if (j < ntile[q]) {
             const int sb = (NS == 2) ? (j & 1) : 0;
             const uint32_t par = (NS == 2) ? ((j >> 1) & 1) : (j & 1);
-            if (!mbar_wait(&bar_p_ready[q * NS + sb], par, abort_p)) { ok = false; break; }
+            if (!mbar_wait_warp(&bar_p_ready[q * NS + sb], par, abort_p)) { ok = false; break; }
             tr.mark(11 + 2 * q);
             tc_fence_after_sync();
-            issue_pv<DP, BN>(o_tm(q), s_tm(q, sb), v_lo(uv), idesc_pv, (j > 0) || (p.first == 0));
-            mma_commit(&bar_pv_done[q]);
+            issue_pv<DP, BN>(o_tm(q), s_tm(q, sb), v_lo(uv), idesc_pv, (j > 0) || (p.first == 0), el);
+            if (NS == 2 || j + 1 == ntile[q]) mma_commit_e(&bar_pv_done[q], el);
             if (NS == 1 && j + 1 < ntile[q]) {
               const int uk = 2 * (j + 1);
-              if (!mbar_wait(&bar_kv_full[slot_of(uk)], par_of(uk), abort_p)) { ok = false; break; }
+              if (!mbar_wait_warp(&bar_kv_full[slot_of(uk)], par_of(uk), abort_p)) { ok = false; break; }
               tc_fence_after_sync();
-              issue_qk<DP, BN>(s_tm(q, 0), q_lo[q], k_lo(uk), idesc_qk);
-              mma_commit(&bar_s_full[q * NS + 0]);
+              issue_qk<DP, BN>(s_tm(q, 0), q_lo[q], k_lo(uk), idesc_qk, el);
+              mma_commit_e(&bar_s_full[q * NS + 0], el);
             }
             tr.mark(12 + 2 * q);
           }
         }
         if (!ok) break;
-        mma_commit(&bar_kv_empty[slot_of(uv)]);
-        if (NS == 1 && j + 1 < nmax) mma_commit(&bar_kv_empty[slot_of(2 * (j + 1))]);
+        mma_commit_e(&bar_kv_empty[slot_of(uv)], el);
+        if (NS == 1 && j + 1 < nmax) mma_commit_e(&bar_kv_empty[slot_of(2 * (j + 1))], el);
       }
     }
     __syncwarp();
@@ -369,7 +374,9 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
           const float alpha = need ? fast_exp2(m_used - m_new) : 1.0f;
           if (need) m_used = m_new;
           l_sum *= alpha;
-          if (j > 0) {
+          // With one score buffer the arrival on bar_s_full that let this iteration start was committed after
+          // O += P_{j-1} V_{j-1} was issued, so that product has retired; with two buffers it has its own barrier.
+          if (NS == 2 && j > 0) {
             if (!mbar_wait_warp(&bar_pv_done[q], (j - 1) & 1, abort_p)) { ok = false; break; }
             tc_fence_after_sync();
           }
@@ -411,7 +418,7 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
       }
 
       // ---- epilogue: wait for the last PV, then spill state or write the result ----
-      if (ok) ok = mbar_wait_warp(&bar_pv_done[q], (n - 1) & 1, abort_p);
+      if (ok) ok = mbar_wait_warp(&bar_pv_done[q], (NS == 2) ? ((n - 1) & 1) : 0, abort_p);
       if (ok) {
         tc_fence_after_sync();
         if (last_here) {

@@ -309,6 +309,73 @@ __device__ __forceinline__ void mma_ts_off(uint32_t d_tmem, uint32_t a_tmem, uin
       : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi), "n"(A_COL_OFF), "n"(B_OFF)
       : "memory");
 }
+// Warp-converged issue.  All 32 lanes of the issuing warp run the surrounding loop (so the descriptor arithmetic is
+// warp-uniform and cheap) and only the lane chosen once by elect_one() executes the instruction.  Measured on B200: an
+// MMA issued from inside a single-lane branch costs the issuing thread 45-95 cycles depending on how busy the other
+// warps of its scheduler are, the converged form 39-54 — the difference between starving and feeding a tensor pipe
+// that retires one 128x128x16 MMA every 64 cycles.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred;
+}
+template <int A_OFF, int B_OFF>
+__device__ __forceinline__ void mma_ss_off_e(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                             uint32_t accumulate, uint32_t elected) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      ".reg .b32 ra, rb;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %8, 0;\n\t"
+      "add.u32 ra, %1, %6;\n\t"
+      "add.u32 rb, %2, %7;\n\t"
+      "mov.b64 da, {ra, %5};\n\t"
+      "mov.b64 db, {rb, %5};\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi), "n"(A_OFF), "n"(B_OFF),
+        "r"(elected)
+      : "memory");
+}
+template <int A_COL_OFF, int B_OFF>
+__device__ __forceinline__ void mma_ts_off_e(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                             uint32_t accumulate, uint32_t elected) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      ".reg .b32 ra, rb;\n\t"
+      ".reg .b64 db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %8, 0;\n\t"
+      "add.u32 ra, %1, %6;\n\t"
+      "add.u32 rb, %2, %7;\n\t"
+      "mov.b64 db, {rb, %5};\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %3, p;\n\t"
+      "}"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi), "n"(A_COL_OFF), "n"(B_OFF),
+        "r"(elected)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_e(uint64_t* bar, uint32_t elected) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}" ::"r"(smem_u32(bar)),
+      "r"(elected)
+      : "memory");
+}
 // Compile-time loop: f(std::integral_constant<int, I>) for I in [0, N).
 template <int I, int N, typename F>
 __device__ __forceinline__ void static_for(F&& f) {
