@@ -68,13 +68,15 @@ __device__ __forceinline__ void issue_qk(uint32_t s_tmem, uint32_t q_smem, uint3
   });
 }
 
-// O[128 x DP] (+)= P[128 x BN] * V[BN x DP]; P in tensor memory, V MN-major.
-template <int DP, int BN>
+// O[128 x DP] (+)= P[128 x BN] * V[BN x DP] over the K-steps [KS0, KS1) of 16 keys each; P in tensor memory,
+// V MN-major.  The product of one K/V tile is issued in kPvParts pieces so that the first keys of P are consumed
+// while the softmax warps still exponentiate the rest of the row.
+template <int DP, int BN, int KS0, int KS1>
 __device__ __forceinline__ void issue_pv(uint32_t o_tmem, uint32_t p_tmem, uint32_t v_smem, uint32_t idesc,
                                          bool accumulate, uint32_t el) {
-  static_for<0, BN / 16>([&](auto ks_) {
+  static_for<KS0, KS1>([&](auto ks_) {
     constexpr int ks = decltype(ks_)::value;
-    mma_ts_off_e<(ks * 8), (ks * 128)>(o_tmem, p_tmem, v_smem, idesc, (accumulate || ks > 0) ? 1u : 0u, el);
+    mma_ts_off_e<(ks * 8), (ks * 128)>(o_tmem, p_tmem, v_smem, idesc, (accumulate || ks > KS0) ? 1u : 0u, el);
   });
 }
 
@@ -91,7 +93,8 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
   __shared__ uint64_t bar_kv_full[kSlots];
   __shared__ uint64_t bar_kv_empty[kSlots];
   __shared__ uint64_t bar_s_full[NQ * NS];
-  __shared__ uint64_t bar_p_ready[NQ * NS];
+  constexpr int kPvParts = BN / 32;  // one hand-off per 32 keys
+  __shared__ uint64_t bar_p_ready[NQ * NS * kPvParts];  // [score buffer][part of the keys]
   __shared__ uint64_t bar_pv_done[NQ];
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
@@ -141,7 +144,7 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
     }
     for (int i = 0; i < NQ * NS; ++i) {
       mbar_init(&bar_s_full[i], 1);
-      mbar_init(&bar_p_ready[i], 128);
+      for (int h = 0; h < kPvParts; ++h) mbar_init(&bar_p_ready[i * kPvParts + h], 128);
     }
     for (int i = 0; i < NQ; ++i) mbar_init(&bar_pv_done[i], 1);
     mbar_fence_init();
@@ -255,10 +258,20 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
           if (j < ntile[q]) {
             const int sb = (NS == 2) ? (j & 1) : 0;
             const uint32_t par = (NS == 2) ? ((j >> 1) & 1) : (j & 1);
-            if (!mbar_wait_warp(&bar_p_ready[q * NS + sb], par, abort_p)) { ok = false; break; }
-            tr.mark(11 + 2 * q);
-            tc_fence_after_sync();
-            issue_pv<DP, BN>(o_tm(q), s_tm(q, sb), v_lo(uv), idesc_pv, (j > 0) || (p.first == 0), el);
+            static_for<0, kPvParts>([&](auto h_) {
+              constexpr int h = decltype(h_)::value;
+              if (ok) {
+                if (!mbar_wait_warp(&bar_p_ready[(q * NS + sb) * kPvParts + h], par, abort_p)) {
+                  ok = false;
+                } else {
+                  if (h == 0) tr.mark(11 + 2 * q);
+                  tc_fence_after_sync();
+                  issue_pv<DP, BN, 2 * h, 2 * h + 2>(o_tm(q), s_tm(q, sb), v_lo(uv), idesc_pv,
+                                                     (h > 0) || (j > 0) || (p.first == 0), el);
+                }
+              }
+            });
+            if (!ok) break;
             if (NS == 2 || j + 1 == ntile[q]) mma_commit_e(&bar_pv_done[q], el);
             if (NS == 1 && j + 1 < ntile[q]) {
               const int uk = 2 * (j + 1);
@@ -408,12 +421,13 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
             u[i] = Pack2<T>::pack(p0, p1);
           }
           tmem_st16(s_addr + c * 16, u);
+          // these 32 keys of P are in place: the issuer may start O += P V on them
+          tmem_st_wait();
+          tc_fence_before_sync();
+          mbar_arrive(&bar_p_ready[(q * NS + sb) * kPvParts + c]);
+          if (c == NCH - 2) tr.mark(24);
         }
         l_sum += (lp[0] + lp[1]) + (lp[2] + lp[3]);
-        tr.mark(24);
-        tmem_st_wait();
-        tc_fence_before_sync();
-        mbar_arrive(&bar_p_ready[q * NS + sb]);
         tr.mark(25);
       }
 
