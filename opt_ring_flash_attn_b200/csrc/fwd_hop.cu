@@ -19,6 +19,10 @@
 #include "common.h"
 #include "tc05.cuh"
 
+#ifndef RFA_FWD_POLY_EVERY
+#define RFA_FWD_POLY_EVERY 4
+#endif
+
 namespace rfa {
 
 struct FwdParams {
@@ -94,6 +98,7 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
   __shared__ uint64_t bar_kv_empty[kSlots];
   __shared__ uint64_t bar_s_full[NQ * NS];
   constexpr int kPvParts = BN / 32;  // one hand-off per 32 keys
+  constexpr int kPolyEvery = RFA_FWD_POLY_EVERY;  // every n-th pair of exponentials on the FMA pipe (0 = none)
   __shared__ uint64_t bar_p_ready[NQ * NS * kPvParts];  // [score buffer][part of the keys]
   __shared__ uint64_t bar_pv_done[NQ];
   __shared__ uint32_t tmem_holder;
@@ -326,6 +331,7 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
         }
         tmem_st_wait();
       }
+      const Exp2Poly exp2_poly;
       // Highest visible local key index for this row.
       const int col_lim = p.causal ? min(row_g, p.kv_len - 1) : (p.kv_len - 1);
 
@@ -406,28 +412,51 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
           tr.mark(23);
         }
 
-        // P = exp2(s * scale_log2 - m_used), packed to 16 bit over the start of S
-        const float neg_m = -m_used;
-        float lp[4] = {0.f, 0.f, 0.f, 0.f};
+        // P = exp2(s * scale_log2 - m_used), packed to 16 bit over the start of S.  Arithmetic runs on packed pairs;
+        // one pair in kPolyEvery takes the polynomial route so that the special-function unit (16 exp2 per clock per
+        // SM, as many cycles per tile as the tensor pipe needs for the two products) is not the only exp2 engine.
+        const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
+        const uint64_t negm2 = pack_f2(-m_used, -m_used);
+        uint64_t lp2[2] = {0ull, 0ull};
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
           uint32_t u[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(r[c][2 * i]), p.scale_log2, neg_m));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(r[c][2 * i + 1]), p.scale_log2, neg_m));
-            lp[(2 * i) & 3] += p0;
-            lp[(2 * i + 1) & 3] += p1;
+            const uint64_t x2 = fma2(pack_u2(r[c][2 * i], r[c][2 * i + 1]), scale2, negm2);
+            uint64_t p2;
+            float p0, p1;
+            if (kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1) {
+              p2 = exp2_poly(x2);
+              unpack_f2(p2, p0, p1);
+            } else {
+              float x0, x1;
+              unpack_f2(x2, x0, x1);
+              p0 = fast_exp2(x0);
+              p1 = fast_exp2(x1);
+              p2 = pack_f2(p0, p1);
+            }
+            lp2[i & 1] = add2(lp2[i & 1], p2);
             u[i] = Pack2<T>::pack(p0, p1);
           }
+          if (c > 0) {
+            // the previous 32 keys of P have landed: the issuer may start O += P V on them
+            tmem_st_wait();
+            tc_fence_before_sync();
+            mbar_arrive(&bar_p_ready[(q * NS + sb) * kPvParts + c - 1]);
+          }
           tmem_st16(s_addr + c * 16, u);
-          // these 32 keys of P are in place: the issuer may start O += P V on them
-          tmem_st_wait();
-          tc_fence_before_sync();
-          mbar_arrive(&bar_p_ready[(q * NS + sb) * kPvParts + c]);
           if (c == NCH - 2) tr.mark(24);
         }
-        l_sum += (lp[0] + lp[1]) + (lp[2] + lp[3]);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        mbar_arrive(&bar_p_ready[(q * NS + sb) * kPvParts + NCH - 1]);
+        {
+          float a0, a1, b0, b1;
+          unpack_f2(lp2[0], a0, a1);
+          unpack_f2(lp2[1], b0, b1);
+          l_sum += (a0 + a1) + (b0 + b1);
+        }
         tr.mark(25);
       }
 

@@ -464,6 +464,67 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Packed pairs of fp32 (Blackwell add/fma .f32x2: one issue slot for two lanes of arithmetic).
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack_u2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void unpack_u2(uint64_t v, uint32_t& lo, uint32_t& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// 2^x for a pair, on the FMA pipe instead of the special-function unit: x = n + f with n = round(x) (magic-number
+// rounding), 2^f by a cubic on [-0.5, 0.5] (relative error 7.5e-5, far below 16-bit rounding of the result), and n
+// added to the exponent field.  x is clamped to >= -125 so that masked (-inf) entries come out as ~2^-125.
+struct Exp2Poly {
+  uint64_t magic, c0, c1, c2, c3;
+  __device__ __forceinline__ Exp2Poly() {
+    magic = pack_f2(12582912.f, 12582912.f);
+    c0 = pack_f2(0.9999281168f, 0.9999281168f);
+    c1 = pack_f2(0.6932609677f, 0.6932609677f);
+    c2 = pack_f2(0.2426108569f, 0.2426108569f);
+    c3 = pack_f2(0.0551714599f, 0.0551714599f);
+  }
+  __device__ __forceinline__ uint64_t operator()(uint64_t x2) const {
+    float x0, x1;
+    unpack_f2(x2, x0, x1);
+    const uint64_t xc = pack_f2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+    const uint64_t xr = add2(xc, magic);        // low mantissa bits = n (two's complement)
+    const uint64_t n = sub2(xr, magic);         // round(x) as a float
+    const uint64_t f = sub2(xc, n);
+    uint64_t pl = fma2(c3, f, c2);
+    pl = fma2(pl, f, c1);
+    pl = fma2(pl, f, c0);
+    uint32_t p0, p1, r0, r1;
+    unpack_u2(pl, p0, p1);
+    unpack_u2(xr, r0, r1);
+    return pack_u2(p0 + (r0 << 23), p1 + (r1 << 23));
+  }
+};
+
 template <typename T>
 struct Pack2;
 template <>
