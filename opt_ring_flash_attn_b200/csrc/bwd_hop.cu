@@ -18,7 +18,8 @@
 //
 // Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 4-11 two elementwise
 // warpgroups (each owns half of the query columns of every tile: P^T, dS^T, then
-// the dV / dK epilogues), warps 12-15 dQ reduction.
+// the dV / dK epilogues), warps 12-19 two dQ reduction warpgroups (half of the
+// query columns each).
 // Tensor memory: [0,BQ) S^T / P^T, [BQ,2BQ) dP^T then dQ^T, then dV (DH) and dK (DH).
 // Head dim 256 runs as two CTAs per tile, each owning 128 columns of dK, dV, dQ.
 #include <stdlib.h>
@@ -28,6 +29,14 @@
 #include "bwd_common.cuh"
 #include "common.h"
 #include "tc05.cuh"
+
+// Pause (ns) a reduction warp takes after each vector reduction.  An SM can push 32 B per clock towards the L2, so
+// the 64 KB of dQ^T of a tile need >= 2048 cycles whatever issues them; unpaced, the eight reduction warps keep the
+// load/store queue full of reductions and every shared-memory or tensor-memory access of the elementwise warps
+// waits behind them.
+#ifndef RFA_RED_SLEEP
+#define RFA_RED_SLEEP 100
+#endif
 
 namespace rfa {
 
@@ -50,7 +59,7 @@ struct BwdCfg {
   // Pad to more than half of the SM's shared memory so that two CTAs never share an SM
   // (each CTA allocates the whole tensor memory).
   static constexpr int kSmemBytes = kSmemUsed < 120 * 1024 ? 120 * 1024 : kSmemUsed;
-  static constexpr int kThreads = 512;
+  static constexpr int kThreads = 640;
   static constexpr int kTmS = 0;
   static constexpr int kTmDP = BQ;
   static constexpr int kTmDV = 2 * BQ;
@@ -60,7 +69,7 @@ struct BwdCfg {
 };
 
 template <int DP, int DH, int BQ, int NST, typename T>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(640, 1)
     bwd_hop_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                    const BwdParams p) {
@@ -123,7 +132,7 @@ __global__ void __launch_bounds__(512, 1)
     mbar_init(&bar_dp_full, 1);
     mbar_init(&bar_ds_ready, 256);
     mbar_init(&bar_dq_full, 1);
-    mbar_init(&bar_dq_drained, 128);
+    mbar_init(&bar_dq_drained, 256);
     mbar_init(&bar_final, 1);
     mbar_fence_init();
   }
@@ -141,13 +150,19 @@ __global__ void __launch_bounds__(512, 1)
   Tracer tr;
   {
     int role = -1;
-    if (lane == 0) role = (warp == 0) ? 0 : (warp == 1) ? 1 : (warp == 4) ? 2 : (warp == 8) ? 3 : (warp == 12) ? 4 : -1;
+    if (lane == 0) role = (warp == 0) ? 0 : (warp == 1) ? 1 : (warp == 4) ? 2 : (warp == 8) ? 3 : (warp == 12) ? 4 : -1;  // (second reduction warpgroup untraced)
     if (role >= 0) tr.init(p.trace, p.trace_ctas, p.trace_cap, kTraceRoles, role);
   }
   auto q_head = [&](int t) { return hkv * G + gs * Gc + t / nI; };
   auto q_tile = [&](int t) { return i_begin + t % nI; };
 
-  if (warp == 0) {
+  // Register budget.  The launch gives every thread 96 registers (640 x 96 = 61440, the pool the warpgroups trade
+  // inside); each role changes its own allowance on entry: 4 service warps x 64, 8 elementwise warps x 128,
+  // 8 reduction warps x 80.  The raise waits until the other roles have lowered theirs, so the sum must fit the pool.
+  static_assert(128 * 64 + 256 * 128 + 256 * 80 <= 640 * 96, "register allowances exceed what the launch allocated");
+  if (warp < 4) {
+   setmaxnreg_dec<64>();
+   if (warp == 0) {
     // =========================== TMA producer ===========================
     if (lane == 0 && run) {
       tma_prefetch_desc(&tm_q);
@@ -186,7 +201,9 @@ __global__ void __launch_bounds__(512, 1)
     __syncwarp();
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
-    if (lane == 0 && run) {
+    // The whole warp runs the loop converged (cheap, warp-uniform descriptor arithmetic); the elected lane issues.
+    if (run) {
+      const uint32_t el = elect_one();
       constexpr uint32_t idesc_s = make_idesc(128, BQ, kBf16, false, false);   // K-major x K-major
       constexpr uint32_t idesc_dv = make_idesc(128, DH, kBf16, false, true);   // A tmem / K-major smem, B MN-major
       constexpr uint32_t idesc_dq = make_idesc(128, BQ, kBf16, true, true);    // both MN-major
@@ -211,16 +228,16 @@ __global__ void __launch_bounds__(512, 1)
         const uint32_t bq = q_km(st);
 #pragma unroll
         for (int ks = 0; ks < DP / 16; ++ks)
-          mma_ss_lo(tm_s, k_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4),
-                    bq + (((ks >> 2) * kPanelQ + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u);
+          mma_ss_lo_e(tm_s, k_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4),
+                    bq + (((ks >> 2) * kPanelQ + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u, el);
       };
       // dP^T[128 x BQ] = V[128 x DP] * dO[BQ x DP]^T
       auto issue_dp = [&](int st) {
         const uint32_t bo = do_km(st);
 #pragma unroll
         for (int ks = 0; ks < DP / 16; ++ks)
-          mma_ss_lo(tm_dp, v_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4),
-                    bo + (((ks >> 2) * kPanelQ + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u);
+          mma_ss_lo_e(tm_dp, v_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4),
+                    bo + (((ks >> 2) * kPanelQ + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u, el);
       };
       // dV[128 x DH] += P^T[128 x BQ] (tensor memory) * dO[BQ x DH]
       auto issue_dv = [&](int st, bool acc) {
@@ -230,7 +247,7 @@ __global__ void __launch_bounds__(512, 1)
           // P^T of query columns [16ks, 16ks+16): each elementwise group packs its half over its own S^T columns
           const int grp = (ks * 16) / (BQ / 2);
           const uint32_t pa = tm_s + grp * (BQ / 2) + ((ks * 16) % (BQ / 2)) / 2;
-          mma_ts_lo(tm_dv, pa, bo + ((ks * 2048) >> 4), idesc_dv, (acc || ks > 0) ? 1u : 0u);
+          mma_ts_lo_e(tm_dv, pa, bo + ((ks * 2048) >> 4), idesc_dv, (acc || ks > 0) ? 1u : 0u, el);
         }
       };
       // dK[128 x DH] += dS^T[128 x BQ] (shared memory, K-major) * Q[BQ x DH]
@@ -238,29 +255,29 @@ __global__ void __launch_bounds__(512, 1)
         const uint32_t bq = q_mn(st);
 #pragma unroll
         for (int ks = 0; ks < BQ / 16; ++ks)
-          mma_ss_lo(tm_dk, ds_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4), bq + ((ks * 2048) >> 4), idesc_dv,
-                    (acc || ks > 0) ? 1u : 0u);
+          mma_ss_lo_e(tm_dk, ds_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4), bq + ((ks * 2048) >> 4), idesc_dv,
+                      (acc || ks > 0) ? 1u : 0u, el);
       };
       // dQ^T[128 (d) x BQ] = K^T[d x 128 (kv)] * dS^T[128 (kv) x BQ]; for head dim 64 the upper 64
       // rows of the A operand run into the V tile (results in those lanes are ignored).
       auto issue_dq = [&]() {
 #pragma unroll
         for (int ks = 0; ks < 128 / 16; ++ks)
-          mma_ss_lo(tm_dp, k_mn + ((ks * 2048) >> 4), ds_mn + ((ks * 2048) >> 4), idesc_dq, ks > 0 ? 1u : 0u);
+          mma_ss_lo_e(tm_dp, k_mn + ((ks * 2048) >> 4), ds_mn + ((ks * 2048) >> 4), idesc_dq, ks > 0 ? 1u : 0u, el);
       };
 
-      bool ok = mbar_wait(&bar_kv_full, 0, abort_p);
-      if (ok) ok = mbar_wait(&bar_q_full[0], 0, abort_p);
+      bool ok = mbar_wait_warp(&bar_kv_full, 0, abort_p);
+      if (ok) ok = mbar_wait_warp(&bar_q_full[0], 0, abort_p);
       if (ok) {
         tc_fence_after_sync();
         issue_s(0);
-        mma_commit(&bar_s_full);
-        ok = mbar_wait(&bar_do_full[0], 0, abort_p);
+        mma_commit_e(&bar_s_full, el);
+        ok = mbar_wait_warp(&bar_do_full[0], 0, abort_p);
       }
       if (ok) {
         tc_fence_after_sync();
         issue_dp(0);
-        mma_commit(&bar_dp_full);
+        mma_commit_e(&bar_dp_full, el);
       }
       for (int t = 0; t < T_total && ok; ++t) {
         const int st = t % NST;
@@ -268,51 +285,56 @@ __global__ void __launch_bounds__(512, 1)
         const uint32_t par_n = ((t + 1) / NST) & 1;
         const bool more = (t + 1 < T_total);
         tr.mark(10);
-        if (!mbar_wait(&bar_p_ready, t & 1, abort_p)) break;
+        if (!mbar_wait_warp(&bar_p_ready, t & 1, abort_p)) break;
         tr.mark(11);
         tc_fence_after_sync();
         issue_dv(st, t > 0);
-        mma_commit(&bar_do_empty[st]);
-        if (NST >= 2 && more) {
-          if (!mbar_wait(&bar_q_full[st_n], par_n, abort_p)) break;
+        mma_commit_e(&bar_do_empty[st], el);
+        // S^T of the next tile goes out now if its Q tile has landed; otherwise after dQ^T / dK, which do not need
+        // it (a blocking wait here would hold back the products the reduction and the next dP^T are waiting for).
+        bool s_issued = !more;
+        if (more && __all_sync(0xffffffffu, mbar_test_wait(&bar_q_full[st_n], par_n))) {
           tr.mark(12);
           tc_fence_after_sync();
           issue_s(st_n);
-          mma_commit(&bar_s_full);
+          mma_commit_e(&bar_s_full, el);
+          s_issued = true;
         }
         tr.mark(13);
-        if (!mbar_wait(&bar_ds_ready, t & 1, abort_p)) break;
+        if (!mbar_wait_warp(&bar_ds_ready, t & 1, abort_p)) break;
         tr.mark(14);
         tc_fence_after_sync();
         issue_dq();  // first: the dQ reduction and the next dP^T wait on it
-        mma_commit(&bar_dq_full);
+        mma_commit_e(&bar_dq_full, el);
         issue_dk(st, t > 0);
-        mma_commit(&bar_q_empty[st]);
+        mma_commit_e(&bar_q_empty[st], el);
         tr.mark(15);
-        if (NST == 1 && more) {
-          if (!mbar_wait(&bar_q_full[st_n], par_n, abort_p)) break;
+        if (!s_issued) {
+          if (!mbar_wait_warp(&bar_q_full[st_n], par_n, abort_p)) break;
           tc_fence_after_sync();
           issue_s(st_n);
-          mma_commit(&bar_s_full);
+          mma_commit_e(&bar_s_full, el);
         }
         if (more) {
-          if (!mbar_wait(&bar_do_full[st_n], par_n, abort_p)) break;
+          if (!mbar_wait_warp(&bar_do_full[st_n], par_n, abort_p)) break;
           tr.mark(16);
-          if (!mbar_wait(&bar_dq_drained, t & 1, abort_p)) break;
+          if (!mbar_wait_warp(&bar_dq_drained, t & 1, abort_p)) break;
           tr.mark(17);
           tc_fence_after_sync();
           issue_dp(st_n);
-          mma_commit(&bar_dp_full);
+          mma_commit_e(&bar_dp_full, el);
           tr.mark(18);
         } else {
-          mma_commit(&bar_final);
+          mma_commit_e(&bar_final, el);
         }
       }
     }
     __syncwarp();
-  } else if (warp >= 4 && warp < 12) {
+   }
+  } else if (warp < 12) {
     // =========================== elementwise warpgroups ===========================
     // Two warpgroups share every tile: group cw owns query columns [cw*BQ/2, (cw+1)*BQ/2).
+    setmaxnreg_inc<128>();
     constexpr int kHalfCols = BQ / 2;
     constexpr int NCH = kHalfCols / 32;  // 32-column chunks per thread
     const int cw = (warp - 4) >> 2;
@@ -467,19 +489,26 @@ __global__ void __launch_bounds__(512, 1)
       }
     }
     __syncwarp();
-  } else if (warp >= 12) {
-    // =========================== dQ reduction warpgroup ===========================
+  } else {
+    // =========================== dQ reduction warpgroups ===========================
+    // Two warpgroups, each owning half of the query columns of dQ^T.  A thread pulls its whole share into registers
+    // with one batch of loads and releases the tensor-memory columns at once (the next dP^T product is waiting for
+    // them); the vector reductions into global memory, which drain at the rate the L2 can add, then overlap the next
+    // tile's products instead of sitting in front of them.
+    setmaxnreg_dec<80>();
+    constexpr int kRedCols = BQ / 2;
+    constexpr int NCR = kRedCols / 32;
+    const int half = (warp - 12) >> 2;
     const int quarter = warp & 3;
     const int drow = quarter * 32 + lane;  // row of dQ^T = head-dim index inside this CTA's half
     const int d = hf * DH + drow;
     const bool d_ok = (drow < DH);
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t a_dq = tmem_base + lane_addr + Cfg::kTmDP;
+    const uint32_t a_dq = tmem_base + lane_addr + Cfg::kTmDP + half * kRedCols;
     // dQ accumulator layout (fp32, private): [b][hq][Spad/128 tiles][32 groups of 4 rows][DP][4].
     // Lane = head-dim index, four consecutive registers = four consecutive query rows, so one
     // 16-byte vector reduction per (lane, row group) and 512 contiguous bytes per warp instruction.
     constexpr size_t kTileElems = static_cast<size_t>(128) * DP;
-    constexpr int NB = BQ / 64;  // batches of two 32-column chunks
     const int nQt128 = p.Spad / 128;
     bool ok = run;
     for (int t = 0; t < T_total && ok; ++t) {
@@ -490,32 +519,28 @@ __global__ void __launch_bounds__(512, 1)
       tr.mark(30);
       tc_fence_after_sync();
       float* base = p.dq_acc + ((static_cast<size_t>(b) * p.Hq + hq) * nQt128 + q0 / 128) * kTileElems +
-                    (static_cast<size_t>((q0 % 128) / 4) * DP + d) * 4;
-#pragma unroll 1
-      for (int bt = 0; bt < NB; ++bt) {
-        uint32_t r0[32], r1[32];
-        tmem_ld32(a_dq + bt * 64, r0);
-        tmem_ld32(a_dq + bt * 64 + 32, r1);
-        tmem_ld_wait32(r0);
-        reg_fence32(r1);
-        if (bt == NB - 1) {
-          // every read of dQ^T has completed: the columns may be overwritten by the next dP^T
-          tc_fence_before_sync();
-          mbar_arrive(&bar_dq_drained);
-          tr.mark(31);
-        }
-        if (d_ok) {
-          // rows beyond Sq and head-dim columns beyond D hold exact zeros (zero-filled operands, P = 0)
+                    (static_cast<size_t>((q0 % 128 + half * kRedCols) / 4) * DP + d) * 4;
+      uint32_t r[NCR][32];
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            red_add_v4_f32(base + static_cast<size_t>(bt * 16 + k) * DP * 4, __uint_as_float(r0[4 * k + 0]) * p.scale,
-                           __uint_as_float(r0[4 * k + 1]) * p.scale, __uint_as_float(r0[4 * k + 2]) * p.scale,
-                           __uint_as_float(r0[4 * k + 3]) * p.scale);
+      for (int c = 0; c < NCR; ++c) tmem_ld32(a_dq + c * 32, r[c]);
+      tmem_ld_wait32(r[0]);
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            red_add_v4_f32(base + static_cast<size_t>(bt * 16 + 8 + k) * DP * 4,
-                           __uint_as_float(r1[4 * k + 0]) * p.scale, __uint_as_float(r1[4 * k + 1]) * p.scale,
-                           __uint_as_float(r1[4 * k + 2]) * p.scale, __uint_as_float(r1[4 * k + 3]) * p.scale);
+      for (int c = 1; c < NCR; ++c) reg_fence32(r[c]);
+      // every read of this half of dQ^T has completed: the columns may be overwritten by the next dP^T
+      tc_fence_before_sync();
+      mbar_arrive(&bar_dq_drained);
+      tr.mark(31);
+      if (d_ok) {
+        // rows beyond Sq and head-dim columns beyond D hold exact zeros (zero-filled operands, P = 0)
+#pragma unroll
+        for (int c = 0; c < NCR; ++c) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            red_add_v4_f32(base + static_cast<size_t>(c * 8 + k) * DP * 4, __uint_as_float(r[c][4 * k + 0]) * p.scale,
+                           __uint_as_float(r[c][4 * k + 1]) * p.scale, __uint_as_float(r[c][4 * k + 2]) * p.scale,
+                           __uint_as_float(r[c][4 * k + 3]) * p.scale);
+            if (RFA_RED_SLEEP > 0) __nanosleep(RFA_RED_SLEEP);
+          }
         }
       }
     }
