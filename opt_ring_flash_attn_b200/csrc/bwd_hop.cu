@@ -34,6 +34,9 @@
 // the 64 KB of dQ^T of a tile need >= 2048 cycles whatever issues them; unpaced, the eight reduction warps keep the
 // load/store queue full of reductions and every shared-memory or tensor-memory access of the elementwise warps
 // waits behind them.
+#ifndef RFA_BWD_POLY_EVERY
+#define RFA_BWD_POLY_EVERY 0
+#endif
 #ifndef RFA_RED_SLEEP
 #define RFA_RED_SLEEP 100
 #endif
@@ -345,6 +348,9 @@ __global__ void __launch_bounds__(640, 1)
     const int col0 = cw * kHalfCols;
     const uint32_t a_s = tmem_base + lane_addr + Cfg::kTmS + col0;
     const uint32_t a_dp = tmem_base + lane_addr + Cfg::kTmDP + col0;
+    constexpr int kPolyEvery = RFA_BWD_POLY_EVERY;  // of the 8 groups of four exponentials per 32 columns
+    const Exp2Poly exp2_poly;
+    const uint64_t nscale2 = pack_f2(-p.scale_log2, -p.scale_log2);
     bool ok = run;
     for (int t = 0; t < T_total && ok; ++t) {
       const int st = t % NST;
@@ -367,7 +373,8 @@ __global__ void __launch_bounds__(640, 1)
 #pragma unroll
         for (int c = 1; c < NCH; ++c) reg_fence32(r[c]);
         tr.mark(21);
-        // P^T = exp2(scale*log2e * S^T - lse2[q]); the causal mask (query before key) only on diagonal tiles
+        // P^T = exp2(scale*log2e * S^T - lse2[q]); the causal mask (query before key) only on diagonal tiles.
+        // Packed pairs: y = lse2 - c*s in one fma, then 2^(-y); every kPolyEvery-th pair on the FMA pipe.
         auto p_phase = [&](auto mask_tag) {
           constexpr bool kMask = decltype(mask_tag)::value;
 #pragma unroll
@@ -375,10 +382,21 @@ __global__ void __launch_bounds__(640, 1)
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               const float4 l4 = *reinterpret_cast<const float4*>(lse2_s + c * 32 + k * 4);
-              float e0 = fast_exp2(fmaf(__uint_as_float(r[c][4 * k + 0]), p.scale_log2, -l4.x));
-              float e1 = fast_exp2(fmaf(__uint_as_float(r[c][4 * k + 1]), p.scale_log2, -l4.y));
-              float e2 = fast_exp2(fmaf(__uint_as_float(r[c][4 * k + 2]), p.scale_log2, -l4.z));
-              float e3 = fast_exp2(fmaf(__uint_as_float(r[c][4 * k + 3]), p.scale_log2, -l4.w));
+              const uint64_t y01 = fma2(pack_u2(r[c][4 * k + 0], r[c][4 * k + 1]), nscale2, pack_f2(l4.x, l4.y));
+              const uint64_t y23 = fma2(pack_u2(r[c][4 * k + 2], r[c][4 * k + 3]), nscale2, pack_f2(l4.z, l4.w));
+              float e0, e1, e2, e3;
+              if (kPolyEvery > 0 && (k % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1) {
+                unpack_f2(exp2_poly.neg(y01), e0, e1);
+                unpack_f2(exp2_poly.neg(y23), e2, e3);
+              } else {
+                float y0, y1, y2, y3;
+                unpack_f2(y01, y0, y1);
+                unpack_f2(y23, y2, y3);
+                e0 = fast_exp2(-y0);
+                e1 = fast_exp2(-y1);
+                e2 = fast_exp2(-y2);
+                e3 = fast_exp2(-y3);
+              }
               if (kMask) {
                 const int qp = q0 + c * 32 + k * 4;
                 if (qp + 0 < kvpos) e0 = 0.f;
@@ -428,10 +446,11 @@ __global__ void __launch_bounds__(640, 1)
             const float4 d4 = *reinterpret_cast<const float4*>(delta_s + c * 32 + k * 4);
             const float2 p01 = Pack2<T>::unpack(pk[c * 16 + 2 * k + 0]);
             const float2 p23 = Pack2<T>::unpack(pk[c * 16 + 2 * k + 1]);
-            const float s0 = p01.x * (__uint_as_float(r[c][4 * k + 0]) - d4.x);
-            const float s1 = p01.y * (__uint_as_float(r[c][4 * k + 1]) - d4.y);
-            const float s2 = p23.x * (__uint_as_float(r[c][4 * k + 2]) - d4.z);
-            const float s3 = p23.y * (__uint_as_float(r[c][4 * k + 3]) - d4.w);
+            float s0, s1, s2, s3;
+            unpack_f2(mul2(pack_f2(p01.x, p01.y),
+                           sub2(pack_u2(r[c][4 * k + 0], r[c][4 * k + 1]), pack_f2(d4.x, d4.y))), s0, s1);
+            unpack_f2(mul2(pack_f2(p23.x, p23.y),
+                           sub2(pack_u2(r[c][4 * k + 2], r[c][4 * k + 3]), pack_f2(d4.z, d4.w))), s2, s3);
             w[2 * k + 0] = Pack2<T>::pack(s0, s1);
             w[2 * k + 1] = Pack2<T>::pack(s2, s3);
           }

@@ -536,6 +536,11 @@ __device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
   asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
@@ -545,13 +550,15 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
 // rounding), 2^f by a cubic on [-0.5, 0.5] (relative error 7.5e-5, far below 16-bit rounding of the result), and n
 // added to the exponent field.  x is clamped to >= -125 so that masked (-inf) entries come out as ~2^-125.
 struct Exp2Poly {
-  uint64_t magic, c0, c1, c2, c3;
+  uint64_t magic, c0, c1, c2, c3, nc1, nc3;
   __device__ __forceinline__ Exp2Poly() {
     magic = pack_f2(12582912.f, 12582912.f);
     c0 = pack_f2(0.9999281168f, 0.9999281168f);
     c1 = pack_f2(0.6932609677f, 0.6932609677f);
     c2 = pack_f2(0.2426108569f, 0.2426108569f);
     c3 = pack_f2(0.0551714599f, 0.0551714599f);
+    nc1 = pack_f2(-0.6932609677f, -0.6932609677f);
+    nc3 = pack_f2(-0.0551714599f, -0.0551714599f);
   }
   __device__ __forceinline__ uint64_t operator()(uint64_t x2) const {
     float x0, x1;
@@ -563,6 +570,22 @@ struct Exp2Poly {
     uint64_t pl = fma2(c3, f, c2);
     pl = fma2(pl, f, c1);
     pl = fma2(pl, f, c0);
+    uint32_t p0, p1, r0, r1;
+    unpack_u2(pl, p0, p1);
+    unpack_u2(xr, r0, r1);
+    return pack_u2(p0 + (r0 << 23), p1 + (r1 << 23));
+  }
+  // 2^(-y) for a pair, for callers that hold the negated exponent.
+  __device__ __forceinline__ uint64_t neg(uint64_t y2) const {
+    float y0, y1;
+    unpack_f2(y2, y0, y1);
+    const uint64_t yc = pack_f2(fminf(y0, 125.f), fminf(y1, 125.f));
+    const uint64_t xr = sub2(magic, yc);        // magic + x
+    const uint64_t n = sub2(xr, magic);         // round(x)
+    const uint64_t g = add2(yc, n);             // -(x - n)
+    uint64_t pl = fma2(nc3, g, c2);
+    pl = fma2(pl, g, nc1);
+    pl = fma2(pl, g, c0);
     uint32_t p0, p1, r0, r1;
     unpack_u2(pl, p0, p1);
     unpack_u2(xr, r0, r1);
