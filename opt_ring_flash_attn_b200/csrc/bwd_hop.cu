@@ -37,6 +37,12 @@
 #ifndef RFA_BWD_POLY_EVERY
 #define RFA_BWD_POLY_EVERY 0
 #endif
+// After dS^T is ready: dK before dQ^T (1) or after it (0).  dK first releases the Q slot ~500 cycles earlier, which
+// matters more than the reduction starting earlier: a Q tile load takes 1500-3000 cycles under the L2 load of the
+// reductions and only two Q stages fit in shared memory.
+#ifndef RFA_BWD_DK_FIRST
+#define RFA_BWD_DK_FIRST 1
+#endif
 #ifndef RFA_RED_SLEEP
 #define RFA_RED_SLEEP 100
 #endif
@@ -293,8 +299,8 @@ __global__ void __launch_bounds__(640, 1)
         tc_fence_after_sync();
         issue_dv(st, t > 0);
         mma_commit_e(&bar_do_empty[st], el);
-        // S^T of the next tile goes out now if its Q tile has landed; otherwise after dQ^T / dK, which do not need
-        // it (a blocking wait here would hold back the products the reduction and the next dP^T are waiting for).
+        // S^T of the next tile goes out now if its Q tile has landed (a non-blocking probe); otherwise it is the first
+        // thing issued once dS^T is ready.
         bool s_issued = !more;
         if (more && __all_sync(0xffffffffu, mbar_test_wait(&bar_q_full[st_n], par_n))) {
           tr.mark(12);
@@ -307,10 +313,26 @@ __global__ void __launch_bounds__(640, 1)
         if (!mbar_wait_warp(&bar_ds_ready, t & 1, abort_p)) break;
         tr.mark(14);
         tc_fence_after_sync();
-        issue_dq();  // first: the dQ reduction and the next dP^T wait on it
+        if (NST >= 2 && !s_issued) {
+          // The elementwise warps have nothing to do until S^T of the next tile exists: it goes first.  (With a single
+          // Q stage the next tile can only be loaded after dK below has released the slot.)
+          if (!mbar_wait_warp(&bar_q_full[st_n], par_n, abort_p)) break;
+          tc_fence_after_sync();
+          issue_s(st_n);
+          mma_commit_e(&bar_s_full, el);
+          s_issued = true;
+        }
+#if RFA_BWD_DK_FIRST
+        issue_dk(st, t > 0);
+        mma_commit_e(&bar_q_empty[st], el);
+        issue_dq();
+        mma_commit_e(&bar_dq_full, el);
+#else
+        issue_dq();
         mma_commit_e(&bar_dq_full, el);
         issue_dk(st, t > 0);
         mma_commit_e(&bar_q_empty[st], el);
+#endif
         tr.mark(15);
         if (!s_issued) {
           if (!mbar_wait_warp(&bar_q_full[st_n], par_n, abort_p)) break;
@@ -549,7 +571,11 @@ __global__ void __launch_bounds__(640, 1)
       tc_fence_before_sync();
       mbar_arrive(&bar_dq_drained);
       tr.mark(31);
+#ifdef RFA_DIAG_NO_RED
+      if (false) {
+#else
       if (d_ok) {
+#endif
         // rows beyond Sq and head-dim columns beyond D hold exact zeros (zero-filled operands, P = 0)
 #pragma unroll
         for (int c = 0; c < NCR; ++c) {
