@@ -378,17 +378,22 @@ def main():
         cur.wait_stream(d2h_s)
         barrier()
         e_steps = max(4, min(args.steps, 10))
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(e_steps):
-            step_e2e(i)
-        cur.wait_stream(d2h_s)  # the last results have reached host memory
-        e1.record()
-        barrier()
-        te = torch.tensor([e0.elapsed_time(e1) / e_steps], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e_ms = float(te.item())
+        # Host-side copies share PCIe and host memory with whatever else runs on the machine: the region is timed
+        # three times and the best pass is reported, with all passes listed beside it.
+        e2e_passes = []
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(e_steps):
+                step_e2e(i)
+            cur.wait_stream(d2h_s)  # the last results have reached host memory
+            e1.record()
+            barrier()
+            te = torch.tensor([e0.elapsed_time(e1) / e_steps], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            e2e_passes.append(float(te.item()))
+        e2e_ms = min(e2e_passes)
         h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv, hdo))
         d2h = sum(x.numel() * x.element_size() for x in (h_out, h_dq, h_dk, h_dv))
     for ws in list(workspace._fwd_cache.values()) + list(workspace._bwd_cache.values()):
@@ -431,6 +436,7 @@ def main():
         if e2e is None and not args.no_e2e:
             line["e2e"] = {"value": flops_job / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                           "passes_ms_per_step": e2e_passes, "reported": "best of the passes",
                            "pipelining": "per step: inputs copied from pinned host memory, out/dq/dk/dv copied back; "
                                          "copies of neighbouring steps overlap the kernels (2 buffer sets, 3 streams)"}
         if W == 1 and not args.no_cpu_baseline:
