@@ -142,6 +142,15 @@ int rfa_bwd_hop_window(const void* q, const void* k, const void* v, const void* 
 int rfa_dkdv_accumulate(const float* prev, const float* block, float* out, size_t n, void* stream);
 
 /*
+ * 16-bit transport of the travelling dK/dV buffer: out[i] = round16(float(prev[i]) + block[i]) for n elements
+ * (n % 8 == 0), prev and out in `dtype` (RFA_DTYPE_BF16 / RFA_DTYPE_FP16), block fp32; prev == NULL writes
+ * round16(block[i]) (first active hop); out may alias prev.  Halves the backward wire bytes at the price of one
+ * rounding per hop.  Replaces `_dkdv_accum_kernel` with a 16-bit comm dtype, selected in the reference by
+ * OPTIMIZED_RING_BWD_COMM_BF16=1 (optimized_ring_flash_attn.py:205-208, 455-475).
+ */
+int rfa_dkdv_accumulate_to16(const void* prev, const float* block, void* out, size_t n, int dtype, void* stream);
+
+/*
  * rfa_bwd_hop for callers that cannot allocate device memory (no counterpart in the reference).
  *
  * Same computation as rfa_bwd_hop followed by rfa_bwd_dq_finalize, but the caller passes no dQ

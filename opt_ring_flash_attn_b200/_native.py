@@ -45,6 +45,7 @@ SIGNATURES = {
     "rfa_noalloc_scratch_bytes": (_sz, []),
     "rfa_bwd_hop_noalloc": (_i, [_vp] * 9 + [_i] * 7 + [_f] + [_i] * 2 + [_vp, _vp]),
     "rfa_dkdv_accumulate": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "rfa_dkdv_accumulate_to16": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
     "rfa_cast_from_f32": (_i, [_vp, _vp, _sz, _i, _vp]),
     "rfa_pack_kv": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "rfa_comm_unique_id": (_i, [_vp]),
@@ -184,6 +185,15 @@ def dkdv_accumulate(prev: torch.Tensor, block: torch.Tensor, out: torch.Tensor, 
     assert prev.dtype == block.dtype == out.dtype == torch.float32 and prev.numel() == block.numel() == out.numel()
     rc = load().rfa_dkdv_accumulate(_ptr(prev), _ptr(block), _ptr(out), prev.numel(), _stream(stream))
     _check(rc, "rfa_dkdv_accumulate")
+
+
+def dkdv_accumulate_to16(prev: Optional[torch.Tensor], block: torch.Tensor, out: torch.Tensor, stream=None) -> None:
+    """``out = round16(float(prev) + block)``; ``prev=None`` writes ``round16(block)``.  16-bit dK/dV transport."""
+    assert block.dtype == torch.float32 and out.dtype in DTYPE_CODES and block.numel() == out.numel()
+    assert prev is None or (prev.dtype == out.dtype and prev.numel() == out.numel())
+    rc = load().rfa_dkdv_accumulate_to16(_ptr(prev), _ptr(block), _ptr(out), block.numel(), DTYPE_CODES[out.dtype],
+                                         _stream(stream))
+    _check(rc, "rfa_dkdv_accumulate_to16")
 
 
 def cast_from_f32(src: torch.Tensor, dst: torch.Tensor, stream=None) -> None:

@@ -187,6 +187,59 @@ __global__ void __launch_bounds__(256) add_f32_kernel(const float4* __restrict__
   }
 }
 
+// Two 16-bit values <-> two floats (round to nearest even on the way down).
+template <typename T>
+struct Cvt16;
+template <>
+struct Cvt16<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
+  }
+};
+template <>
+struct Cvt16<__half> {
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&u));
+  }
+};
+
+// out16 = round(float(prev16) + block32) over groups of 8 elements (prev may be null: out16 = round(block32)).
+// Streams 32 + 16 + 16 bytes per group: HBM-bound.
+template <typename T, bool kHasPrev>
+__global__ void __launch_bounds__(256) accum_to16_kernel(const uint4* __restrict__ prev, const float4* __restrict__ block,
+                                                        uint4* out, size_t n8) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    const float4 a = block[2 * i];
+    const float4 b = block[2 * i + 1];
+    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    if (kHasPrev) {
+      const uint4 pw = prev[i];
+      const uint32_t w[4] = {pw.x, pw.y, pw.z, pw.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = Cvt16<T>::unpack(w[k]);
+        v[2 * k] += f.x;
+        v[2 * k + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = Cvt16<T>::pack(v[0], v[1]);
+    o.y = Cvt16<T>::pack(v[2], v[3]);
+    o.z = Cvt16<T>::pack(v[4], v[5]);
+    o.w = Cvt16<T>::pack(v[6], v[7]);
+    out[i] = o;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) cast_from_f32_kernel(const float* __restrict__ src, T* __restrict__ dst,
                                                            size_t n8, size_t n) {
@@ -295,6 +348,34 @@ extern "C" int rfa_dkdv_accumulate(const float* prev, const float* block, float*
   if (blocks > 148u * 16) blocks = 148u * 16;
   add_f32_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const float4*>(prev), reinterpret_cast<const float4*>(block), reinterpret_cast<float4*>(out), n4);
+  return cuda_status(cudaGetLastError());
+}
+
+extern "C" int rfa_dkdv_accumulate_to16(const void* prev, const float* block, void* out, size_t n, int dtype,
+                                        void* stream) {
+  using namespace rfa;
+  if (!block || !out) return RFA_ERR_INVALID_ARG;
+  if (dtype != RFA_DTYPE_BF16 && dtype != RFA_DTYPE_FP16) return RFA_ERR_UNSUPPORTED;
+  if (n == 0) return RFA_OK;
+  if (n % 8) return RFA_ERR_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(block) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u) ||
+      (reinterpret_cast<uintptr_t>(prev) & 15u))
+    return RFA_ERR_INVALID_ARG;
+  const size_t n8 = n / 8;
+  size_t blocks = (n8 + 255) / 256;
+  if (blocks > 148u * 16) blocks = 148u * 16;
+  const unsigned g = static_cast<unsigned>(blocks);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const uint4* p4 = static_cast<const uint4*>(prev);
+  const float4* b4 = reinterpret_cast<const float4*>(block);
+  uint4* o4 = static_cast<uint4*>(out);
+  if (dtype == RFA_DTYPE_BF16) {
+    if (prev) accum_to16_kernel<__nv_bfloat16, true><<<g, 256, 0, s>>>(p4, b4, o4, n8);
+    else accum_to16_kernel<__nv_bfloat16, false><<<g, 256, 0, s>>>(p4, b4, o4, n8);
+  } else {
+    if (prev) accum_to16_kernel<__half, true><<<g, 256, 0, s>>>(p4, b4, o4, n8);
+    else accum_to16_kernel<__half, false><<<g, 256, 0, s>>>(p4, b4, o4, n8);
+  }
   return cuda_status(cudaGetLastError());
 }
 

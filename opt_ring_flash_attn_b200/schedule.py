@@ -18,6 +18,7 @@ dQ, dK and dV of a hop come from one fused kernel.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -78,12 +79,42 @@ def ring_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softm
     return out, lse
 
 
+def backward_comm_dtype(local_dtype: torch.dtype) -> torch.dtype:
+    """Dtype of the travelling dK/dV buffers: fp32, or the input dtype when ``OPTIMIZED_RING_BWD_COMM_BF16=1`` — the
+    reference's own switch and semantics (optimized_ring_flash_attn.py:205-208): the partial sums are rounded to 16 bit
+    once per hop and the backward wire bytes halve."""
+    if os.getenv("OPTIMIZED_RING_BWD_COMM_BF16", "0") == "1" and local_dtype in (torch.bfloat16, torch.float16):
+        return local_dtype
+    return torch.float32
+
+
+def _fold_block(kn, buf, block, first: bool) -> None:
+    """Travelling buffer (+)= this hop's fp32 block, in the buffer's dtype."""
+    if buf.dtype == torch.float32:
+        if first:
+            buf.copy_(block)
+        else:
+            kn.dkdv_accumulate(buf, block, buf)
+    else:
+        kn.dkdv_accumulate_to16(None if first else buf, block, buf)
+
+
+def _finish_dkdv(kn, final, dk, dv) -> None:
+    if final.dtype == torch.float32:
+        kn.cast_from_f32(final[0], dk)
+        kn.cast_from_f32(final[1], dv)
+    else:  # already in the input dtype; copied because the buffer belongs to the cached workspace
+        dk.copy_(final[0])
+        dv.copy_(final[1])
+
+
 def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
                   lse: torch.Tensor, softmax_scale: float, causal: bool, kernels=None):
     """Returns ``(dq, dk, dv)`` in the input dtypes."""
     kn = kernels if kernels is not None else _native
     W, rank = _world(group)
-    ws = workspace.backward_workspace(q, k, W)
+    ws = workspace.backward_workspace(q, k, W, backward_comm_dtype(q.dtype))
+    wire16 = ws.dkdv[0].dtype != torch.float32
     dout = dout.contiguous()
     kn.bwd_prepare(out, dout, lse, ws.delta, ws.lse2, ws.dq_acc, ws.status)
 
@@ -111,14 +142,17 @@ def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
         buf = ws.dkdv[prev_slot]
         active = (not causal) or step <= rank
         if active:
-            # The hop kernel does not wait for the ring: on step 0 it writes the travelling buffer directly,
-            # later it writes this rank's block and the partial sums are folded in once they have arrived.
-            kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, buf if step == 0 else ws.block_dkdv,
+            # The hop kernel does not wait for the ring: on step 0 it writes the travelling buffer directly (fp32
+            # transport), later it writes this rank's block and the partial sums are folded in once they have arrived.
+            direct = step == 0 and not wire16
+            kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, buf if direct else ws.block_dkdv,
                        softmax_scale, False, causal and step == 0, ws.status)
+            if step == 0 and wire16:
+                _fold_block(kn, buf, ws.block_dkdv, first=True)
         if step > 0:
             dkv_comm.wait()  # partial dK/dV of the block now held has arrived in dkdv[prev_slot]
             if active:
-                kn.dkdv_accumulate(buf, ws.block_dkdv, buf)
+                _fold_block(kn, buf, ws.block_dkdv, first=False)
         if step + 1 < W:
             kv_comm.wait()
             cur = ws.kv_recv[step & 1]
@@ -127,8 +161,7 @@ def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
     dkv_comm.wait()
     final = ws.dkdv[(W - 1) & 1]
     kn.dq_finalize(ws.dq_acc, dq)
-    kn.cast_from_f32(final[0], dk)
-    kn.cast_from_f32(final[1], dv)
+    _finish_dkdv(kn, final, dk, dv)
     return dq, dk, dv
 
 
@@ -194,7 +227,8 @@ def zigzag_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
         return ring_backward(group, dout, q, k, v, out, lse, softmax_scale, True, kernels=kernels)
     S = q.shape[1]
     half = _zigzag_half(S)
-    ws = workspace.backward_workspace(q, k, W)
+    ws = workspace.backward_workspace(q, k, W, backward_comm_dtype(q.dtype))
+    wire16 = ws.dkdv[0].dtype != torch.float32
     dout = dout.contiguous()
     kn.bwd_prepare(out, dout, lse, ws.delta, ws.lse2, ws.dq_acc, ws.status)
     dq = torch.empty_like(q)
@@ -211,8 +245,10 @@ def zigzag_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
         prev_slot = (step - 1) & 1
         buf = ws.dkdv[prev_slot]
         if step == 0:
-            kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, buf, softmax_scale, False, True,
-                       ws.status, q_begin=0, kv_len=S)
+            kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, ws.block_dkdv if wire16 else buf,
+                       softmax_scale, False, True, ws.status, q_begin=0, kv_len=S)
+            if wire16:
+                _fold_block(kn, buf, ws.block_dkdv, first=True)
         elif step <= rank:
             kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, ws.block_dkdv, softmax_scale, False,
                        False, ws.status, q_begin=0, kv_len=half)
@@ -221,7 +257,7 @@ def zigzag_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
                        False, ws.status, q_begin=half, kv_len=S)
         if step > 0:
             dkv_comm.wait()
-            kn.dkdv_accumulate(buf, ws.block_dkdv, buf)
+            _fold_block(kn, buf, ws.block_dkdv, first=False)
         if step + 1 < W:
             kv_comm.wait()
             cur = ws.kv_recv[step & 1]
@@ -230,6 +266,5 @@ def zigzag_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
     dkv_comm.wait()
     final = ws.dkdv[(W - 1) & 1]
     kn.dq_finalize(ws.dq_acc, dq)
-    kn.cast_from_f32(final[0], dk)
-    kn.cast_from_f32(final[1], dv)
+    _finish_dkdv(kn, final, dk, dv)
     return dq, dk, dv

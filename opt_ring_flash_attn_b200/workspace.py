@@ -39,7 +39,7 @@ class BackwardWorkspace:
     delta: torch.Tensor               # fp32 [B, Hq, Spad]
     lse2: torch.Tensor                # fp32 [B, Hq, Spad]
     dq_acc: torch.Tensor              # fp32, private tiled layout (B*Hq*Spad*padded D elements)
-    dkdv: List[torch.Tensor]          # 2 x fp32 [2, B, S, Hkv, D] (1 slot when world size is 1)
+    dkdv: List[torch.Tensor]          # 2 x [2, B, S, Hkv, D] in the transport dtype, fp32 by default (1 fp32 slot when world size is 1)
     block_dkdv: Optional[torch.Tensor]  # fp32 [2, B, S, Hkv, D]: this hop's own dK/dV before the ring accumulate
     kv_send: Optional[torch.Tensor]
     kv_recv: List[torch.Tensor]
@@ -50,8 +50,8 @@ _fwd_cache: Dict[Tuple, ForwardWorkspace] = {}
 _bwd_cache: Dict[Tuple, BackwardWorkspace] = {}
 
 
-def _key(q: torch.Tensor, k: torch.Tensor, world_size: int) -> Tuple:
-    return (tuple(q.shape), tuple(k.shape), q.dtype, str(q.device), world_size)
+def _key(q: torch.Tensor, k: torch.Tensor, world_size: int, extra=None) -> Tuple:
+    return (tuple(q.shape), tuple(k.shape), q.dtype, str(q.device), world_size, extra)
 
 
 def forward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int) -> ForwardWorkspace:
@@ -78,8 +78,13 @@ def forward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int) -> Forw
     return ws
 
 
-def backward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int) -> BackwardWorkspace:
-    key = _key(q, k, world_size)
+def backward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int,
+                       comm_dtype: torch.dtype = torch.float32) -> BackwardWorkspace:
+    """``comm_dtype`` is the dtype of the travelling dK/dV buffers (fp32, or the input dtype for 16-bit transport,
+    optimized_ring_flash_attn.py:205-208, 271-272); this hop's own block is always fp32."""
+    if world_size == 1:
+        comm_dtype = torch.float32
+    key = _key(q, k, world_size, comm_dtype)
     ws = _bwd_cache.get(key)
     if ws is not None:
         return ws
@@ -91,13 +96,13 @@ def backward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int) -> Bac
     lse2 = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
     dq_acc = torch.empty(B * Hq * spad * _padded_head_dim(D), dtype=torch.float32, device=dev)
     nslots = 1 if world_size == 1 else 2
-    dkdv = [torch.empty(2, B, S, Hkv, D, dtype=torch.float32, device=dev) for _ in range(nslots)]
+    dkdv = [torch.empty(2, B, S, Hkv, D, dtype=comm_dtype, device=dev) for _ in range(nslots)]
     if world_size == 1:
         kv_send, kv_recv, block_dkdv = None, [], None
     else:
         kv_send = torch.empty(2, B, S, Hkv, D, dtype=q.dtype, device=dev)
         kv_recv = [torch.empty_like(kv_send) for _ in range(2)]
-        block_dkdv = torch.empty_like(dkdv[0])
+        block_dkdv = torch.empty(2, B, S, Hkv, D, dtype=torch.float32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     ws = BackwardWorkspace(delta, lse2, dq_acc, dkdv, block_dkdv, kv_send, kv_recv, status)
     _bwd_cache.clear()

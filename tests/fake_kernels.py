@@ -119,5 +119,9 @@ def dkdv_accumulate(prev, block, out, stream=None):
     out.copy_(prev + block)
 
 
+def dkdv_accumulate_to16(prev, block, out, stream=None):
+    out.copy_((block if prev is None else prev.float() + block).to(out.dtype))
+
+
 def cast_from_f32(src, dst, stream=None):
     dst.copy_(src.to(dst.dtype))

@@ -172,6 +172,22 @@ def test_dkdv_accumulate():
     assert torch.equal(a, ref)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_dkdv_accumulate_to16(dtype):
+    """16-bit dK/dV transport: out = round(float(prev) + block), bit-exact against torch (same rounding mode)."""
+    from opt_ring_flash_attn_b200 import _native
+
+    dev = torch.device("cuda:0")
+    block = torch.randn(2, 1, 200, 2, 96, device=dev)
+    out = torch.empty_like(block, dtype=dtype)
+    _native.dkdv_accumulate_to16(None, block, out)  # first active hop
+    assert torch.equal(out, block.to(dtype))
+    prev = torch.randn_like(block).to(dtype)
+    ref = (prev.float() + block).to(dtype)
+    _native.dkdv_accumulate_to16(prev, block, prev)  # in place, as the ring schedule uses it
+    assert torch.equal(prev, ref)
+
+
 def test_abi_rejects_bad_arguments():
     from opt_ring_flash_attn_b200 import _native
 

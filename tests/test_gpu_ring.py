@@ -32,6 +32,8 @@ def _worker(rank, world, port, cfg, errs):
 
         B, S, Hq, Hkv, D, causal, dtype = cfg[:7]
         zigzag = len(cfg) > 7 and cfg[7]
+        wire16 = len(cfg) > 8 and cfg[8]  # dK/dV travel in the input dtype (the reference's OPTIMIZED_RING_BWD_COMM_BF16)
+        os.environ["OPTIMIZED_RING_BWD_COMM_BF16"] = "1" if wire16 else "0"
         q, k, v, dout = (x.to(dev) for x in make_inputs(60, B, S * world, Hq, Hkv, D, dtype=dtype))
         if zigzag:
             qs, ks, vs, dos = (zigzag_shard(x, world) for x in (q, k, v, dout))
@@ -45,6 +47,8 @@ def _worker(rank, world, port, cfg, errs):
         torch.cuda.synchronize()
         for ws in list(workspace._fwd_cache.values()) + list(workspace._bwd_cache.values()):
             _native.check_status(ws.status, "ring")
+        if wire16:
+            assert next(iter(workspace._bwd_cache.values())).dkdv[0].dtype == dtype
         if zigzag:
             ref = zigzag_oracle(q, k, v, dout, world, head_chunk=4)
         else:
@@ -72,6 +76,7 @@ def _worker(rank, world, port, cfg, errs):
     (2, 256, 4, 2, 64, True, torch.float16),
     (1, 320, 2, 2, 256, True, torch.bfloat16),
     (1, 512, 4, 2, 128, True, torch.bfloat16, True),  # zigzag layout
+    (1, 384, 4, 2, 128, True, torch.bfloat16, False, True),  # 16-bit dK/dV transport
 ])
 def test_ring_nccl(cfg):
     import torch.multiprocessing as mp

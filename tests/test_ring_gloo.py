@@ -17,7 +17,9 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, causal, Hq, Hkv, use_subgroup, errs):
+def _worker(rank, world, port, causal, Hq, Hkv, use_subgroup, errs, wire16=False):
+    # 16-bit dK/dV transport is switched on like in the reference (optimized_ring_flash_attn.py:205-208)
+    os.environ["OPTIMIZED_RING_BWD_COMM_BF16"] = "1" if wire16 else "0"
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -54,6 +56,10 @@ def _worker(rank, world, port, causal, Hq, Hkv, use_subgroup, errs):
         def rel(a, b):
             return ((a.float() - b).norm() / b.norm()).item()
 
+        if wire16 and ring_world > 1:
+            from opt_ring_flash_attn_b200 import workspace
+            ws = next(iter(workspace._bwd_cache.values()))
+            assert ws.dkdv[0].dtype == torch.bfloat16 and ws.block_dkdv.dtype == torch.float32
         assert torch.equal(out, out2)
         assert (out.float() - ref["out"][r]).abs().max().item() <= 1e-2
         assert (lse[:, :, :S] - ref["lse"][r]).abs().max().item() <= 1e-3
@@ -68,13 +74,15 @@ def _worker(rank, world, port, causal, Hq, Hkv, use_subgroup, errs):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,causal,Hq,Hkv,sub", [(2, True, 2, 2, False), (2, False, 4, 2, False),
-                                                     (3, True, 4, 2, False), (3, True, 2, 1, True)])
-def test_ring_schedules_on_gloo(world, causal, Hq, Hkv, sub):
+@pytest.mark.parametrize("world,causal,Hq,Hkv,sub,wire16", [(2, True, 2, 2, False, False), (2, False, 4, 2, False, False),
+                                                            (3, True, 4, 2, False, False), (3, True, 2, 1, True, False),
+                                                            (3, True, 4, 2, False, True), (2, False, 2, 2, False, True)])
+def test_ring_schedules_on_gloo(world, causal, Hq, Hkv, sub, wire16):
     ctx = mp.get_context("spawn")
     errs = ctx.SimpleQueue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, causal, Hq, Hkv, sub, errs)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, causal, Hq, Hkv, sub, errs, wire16))
+             for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
@@ -89,7 +97,8 @@ def test_ring_schedules_on_gloo(world, causal, Hq, Hkv, sub):
     assert not msgs and all(p.exitcode == 0 for p in procs), msgs
 
 
-def _zz_worker(rank, world, port, Hq, Hkv, errs):
+def _zz_worker(rank, world, port, Hq, Hkv, errs, wire16=False):
+    os.environ["OPTIMIZED_RING_BWD_COMM_BF16"] = "1" if wire16 else "0"
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -126,12 +135,12 @@ def _zz_worker(rank, world, port, Hq, Hkv, errs):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,Hq,Hkv", [(2, 2, 2), (3, 4, 2)])
-def test_zigzag_schedules_on_gloo(world, Hq, Hkv):
+@pytest.mark.parametrize("world,Hq,Hkv,wire16", [(2, 2, 2, False), (3, 4, 2, False), (3, 4, 2, True)])
+def test_zigzag_schedules_on_gloo(world, Hq, Hkv, wire16):
     ctx = mp.get_context("spawn")
     errs = ctx.SimpleQueue()
     port = _free_port()
-    procs = [ctx.Process(target=_zz_worker, args=(r, world, port, Hq, Hkv, errs)) for r in range(world)]
+    procs = [ctx.Process(target=_zz_worker, args=(r, world, port, Hq, Hkv, errs, wire16)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
