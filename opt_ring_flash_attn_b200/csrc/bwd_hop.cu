@@ -159,7 +159,8 @@ __global__ void __launch_bounds__(640, 1)
   Tracer tr;
   {
     int role = -1;
-    if (lane == 0) role = (warp == 0) ? 0 : (warp == 1) ? 1 : (warp == 4) ? 2 : (warp == 8) ? 3 : (warp == 12) ? 4 : -1;  // (second reduction warpgroup untraced)
+    // traced roles: producer, issuer, one warp of each elementwise group, one reduction warp
+    if (lane == 0) role = (warp == 0) ? 0 : (warp == 1) ? 1 : (warp == 4) ? 2 : (warp == 8) ? 3 : (warp == 12) ? 4 : -1;
     if (role >= 0) tr.init(p.trace, p.trace_ctas, p.trace_cap, kTraceRoles, role);
   }
   auto q_head = [&](int t) { return hkv * G + gs * Gc + t / nI; };
@@ -170,192 +171,196 @@ __global__ void __launch_bounds__(640, 1)
   // 8 reduction warps x 80.  The raise waits until the other roles have lowered theirs, so the sum must fit the pool.
   static_assert(128 * 64 + 256 * 128 + 256 * 80 <= 640 * 96, "register allowances exceed what the launch allocated");
   if (warp < 4) {
-   setmaxnreg_dec<64>();
-   if (warp == 0) {
-    // =========================== TMA producer ===========================
-    if (lane == 0 && run) {
-      tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
-      tma_prefetch_desc(&tm_do);
-      mbar_expect_tx(&bar_kv_full, 2 * Cfg::kKBytes);
+    setmaxnreg_dec<64>();
+    if (warp == 0) {
+      // =========================== TMA producer ===========================
+      if (lane == 0 && run) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+        tma_prefetch_desc(&tm_do);
+        mbar_expect_tx(&bar_kv_full, 2 * Cfg::kKBytes);
 #pragma unroll
-      for (int pn = 0; pn < Cfg::kPanels; ++pn) {
-        tma_load_4d(s_k + pn * kPanelK, &tm_k, &bar_kv_full, pn * 64, hkv, n0, b);
-        tma_load_4d(s_v + pn * kPanelK, &tm_v, &bar_kv_full, pn * 64, hkv, n0, b);
+        for (int pn = 0; pn < Cfg::kPanels; ++pn) {
+          tma_load_4d(s_k + pn * kPanelK, &tm_k, &bar_kv_full, pn * 64, hkv, n0, b);
+          tma_load_4d(s_v + pn * kPanelK, &tm_v, &bar_kv_full, pn * 64, hkv, n0, b);
+        }
+        for (int t = 0; t < T_total; ++t) {
+          const int st = t % NST;
+          const uint32_t par_empty = ((t / NST) & 1) ^ 1;
+          const int hq = q_head(t);
+          const int i = q_tile(t);
+          // dO first: its slot frees earlier (after the dV product) than the Q slot (after dK).
+          if (!mbar_wait(&bar_do_empty[st], par_empty, abort_p)) break;
+          tr.mark(40);
+          mbar_expect_tx(&bar_do_full[st], Cfg::kQBytes);
+#pragma unroll
+          for (int pn = 0; pn < Cfg::kPanels; ++pn)
+            tma_load_4d(s_do + st * Cfg::kQBytes + pn * kPanelQ, &tm_do, &bar_do_full[st], pn * 64, hq, i * BQ, b);
+          if (!mbar_wait(&bar_q_empty[st], par_empty, abort_p)) break;
+          tr.mark(41);
+          mbar_expect_tx(&bar_q_full[st], Cfg::kQBytes + Cfg::kStatBytes);
+#pragma unroll
+          for (int pn = 0; pn < Cfg::kPanels; ++pn)
+            tma_load_4d(s_q + st * Cfg::kQBytes + pn * kPanelQ, &tm_q, &bar_q_full[st], pn * 64, hq, i * BQ, b);
+          const size_t stat_off = (static_cast<size_t>(b) * p.Hq + hq) * p.Spad + static_cast<size_t>(i) * BQ;
+          bulk_load_1d(s_stat + st * Cfg::kStatBytes, p.lse2 + stat_off, BQ * 4, &bar_q_full[st]);
+          bulk_load_1d(s_stat + st * Cfg::kStatBytes + BQ * 4, p.delta + stat_off, BQ * 4, &bar_q_full[st]);
+        }
       }
-      for (int t = 0; t < T_total; ++t) {
-        const int st = t % NST;
-        const uint32_t par_empty = ((t / NST) & 1) ^ 1;
-        const int hq = q_head(t);
-        const int i = q_tile(t);
-        // dO first: its slot frees earlier (after the dV product) than the Q slot (after dK).
-        if (!mbar_wait(&bar_do_empty[st], par_empty, abort_p)) break;
-        tr.mark(40);
-        mbar_expect_tx(&bar_do_full[st], Cfg::kQBytes);
-#pragma unroll
-        for (int pn = 0; pn < Cfg::kPanels; ++pn)
-          tma_load_4d(s_do + st * Cfg::kQBytes + pn * kPanelQ, &tm_do, &bar_do_full[st], pn * 64, hq, i * BQ, b);
-        if (!mbar_wait(&bar_q_empty[st], par_empty, abort_p)) break;
-        tr.mark(41);
-        mbar_expect_tx(&bar_q_full[st], Cfg::kQBytes + Cfg::kStatBytes);
-#pragma unroll
-        for (int pn = 0; pn < Cfg::kPanels; ++pn)
-          tma_load_4d(s_q + st * Cfg::kQBytes + pn * kPanelQ, &tm_q, &bar_q_full[st], pn * 64, hq, i * BQ, b);
-        const size_t stat_off = (static_cast<size_t>(b) * p.Hq + hq) * p.Spad + static_cast<size_t>(i) * BQ;
-        bulk_load_1d(s_stat + st * Cfg::kStatBytes, p.lse2 + stat_off, BQ * 4, &bar_q_full[st]);
-        bulk_load_1d(s_stat + st * Cfg::kStatBytes + BQ * 4, p.delta + stat_off, BQ * 4, &bar_q_full[st]);
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // =========================== MMA issuer ===========================
-    // The whole warp runs the loop converged (cheap, warp-uniform descriptor arithmetic); the elected lane issues.
-    if (run) {
-      const uint32_t el = elect_one();
-      constexpr uint32_t idesc_s = make_idesc(128, BQ, kBf16, false, false);   // K-major x K-major
-      constexpr uint32_t idesc_dv = make_idesc(128, DH, kBf16, false, true);   // A tmem / K-major smem, B MN-major
-      constexpr uint32_t idesc_dq = make_idesc(128, BQ, kBf16, true, true);    // both MN-major
-      const uint32_t tm_s = tmem_base + Cfg::kTmS;
-      const uint32_t tm_dp = tmem_base + Cfg::kTmDP;
-      const uint32_t tm_dv = tmem_base + Cfg::kTmDV;
-      const uint32_t tm_dk = tmem_base + Cfg::kTmDK;
+      __syncwarp();
+    } else if (warp == 1) {
+      // =========================== MMA issuer ===========================
+      // The whole warp runs the loop converged (cheap, warp-uniform descriptor arithmetic); the elected lane issues.
+      if (run) {
+        const uint32_t el = elect_one();
+        constexpr uint32_t idesc_s = make_idesc(128, BQ, kBf16, false, false);   // K-major x K-major
+        constexpr uint32_t idesc_dv = make_idesc(128, DH, kBf16, false, true);   // A tmem / K-major smem, B MN-major
+        constexpr uint32_t idesc_dq = make_idesc(128, BQ, kBf16, true, true);    // both MN-major
+        const uint32_t tm_s = tmem_base + Cfg::kTmS;
+        const uint32_t tm_dp = tmem_base + Cfg::kTmDP;
+        const uint32_t tm_dv = tmem_base + Cfg::kTmDV;
+        const uint32_t tm_dk = tmem_base + Cfg::kTmDK;
 
-      // Descriptor low words of the resident tiles; offsets below are in 16-byte units.
-      const uint32_t k_km = desc_lo_kmajor(s_k);                                   // K as K-major A (S^T)
-      const uint32_t v_km = desc_lo_kmajor(s_v);                                   // V as K-major A (dP^T)
-      const uint32_t k_mn = desc_lo_mnmajor(s_k + hf * (DH / 64) * kPanelK, kPanelK);  // K^T as MN-major A (dQ^T)
-      const uint32_t ds_km = desc_lo_kmajor(s_ds);                                 // dS^T as K-major A (dK)
-      const uint32_t ds_mn = desc_lo_mnmajor(s_ds, kPanelK);                       // dS^T as MN-major B (dQ^T)
-      auto q_km = [&](int st) { return desc_lo_kmajor(s_q + st * Cfg::kQBytes); };
-      auto do_km = [&](int st) { return desc_lo_kmajor(s_do + st * Cfg::kQBytes); };
-      auto q_mn = [&](int st) { return desc_lo_mnmajor(s_q + st * Cfg::kQBytes + hf * (DH / 64) * kPanelQ, kPanelQ); };
-      auto do_mn = [&](int st) { return desc_lo_mnmajor(s_do + st * Cfg::kQBytes + hf * (DH / 64) * kPanelQ, kPanelQ); };
+        // Descriptor low words of the resident tiles; offsets below are in 16-byte units.
+        const uint32_t k_km = desc_lo_kmajor(s_k);                                   // K as K-major A (S^T)
+        const uint32_t v_km = desc_lo_kmajor(s_v);                                   // V as K-major A (dP^T)
+        const uint32_t k_mn = desc_lo_mnmajor(s_k + hf * (DH / 64) * kPanelK, kPanelK);  // K^T as MN-major A (dQ^T)
+        const uint32_t ds_km = desc_lo_kmajor(s_ds);                                 // dS^T as K-major A (dK)
+        const uint32_t ds_mn = desc_lo_mnmajor(s_ds, kPanelK);                       // dS^T as MN-major B (dQ^T)
+        auto q_km = [&](int st) { return desc_lo_kmajor(s_q + st * Cfg::kQBytes); };
+        auto do_km = [&](int st) { return desc_lo_kmajor(s_do + st * Cfg::kQBytes); };
+        auto q_mn = [&](int st) {
+          return desc_lo_mnmajor(s_q + st * Cfg::kQBytes + hf * (DH / 64) * kPanelQ, kPanelQ);
+        };
+        auto do_mn = [&](int st) {
+          return desc_lo_mnmajor(s_do + st * Cfg::kQBytes + hf * (DH / 64) * kPanelQ, kPanelQ);
+        };
 
-      // S^T[128 x BQ] = K[128 x DP] * Q[BQ x DP]^T
-      auto issue_s = [&](int st) {
-        const uint32_t bq = q_km(st);
+        // S^T[128 x BQ] = K[128 x DP] * Q[BQ x DP]^T
+        auto issue_s = [&](int st) {
+          const uint32_t bq = q_km(st);
 #pragma unroll
-        for (int ks = 0; ks < DP / 16; ++ks)
-          mma_ss_lo_e(tm_s, k_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4),
-                    bq + (((ks >> 2) * kPanelQ + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u, el);
-      };
-      // dP^T[128 x BQ] = V[128 x DP] * dO[BQ x DP]^T
-      auto issue_dp = [&](int st) {
-        const uint32_t bo = do_km(st);
+          for (int ks = 0; ks < DP / 16; ++ks)
+            mma_ss_lo_e(tm_s, k_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4),
+                      bq + (((ks >> 2) * kPanelQ + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u, el);
+        };
+        // dP^T[128 x BQ] = V[128 x DP] * dO[BQ x DP]^T
+        auto issue_dp = [&](int st) {
+          const uint32_t bo = do_km(st);
 #pragma unroll
-        for (int ks = 0; ks < DP / 16; ++ks)
-          mma_ss_lo_e(tm_dp, v_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4),
-                    bo + (((ks >> 2) * kPanelQ + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u, el);
-      };
-      // dV[128 x DH] += P^T[128 x BQ] (tensor memory) * dO[BQ x DH]
-      auto issue_dv = [&](int st, bool acc) {
-        const uint32_t bo = do_mn(st);
+          for (int ks = 0; ks < DP / 16; ++ks)
+            mma_ss_lo_e(tm_dp, v_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4),
+                      bo + (((ks >> 2) * kPanelQ + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u, el);
+        };
+        // dV[128 x DH] += P^T[128 x BQ] (tensor memory) * dO[BQ x DH]
+        auto issue_dv = [&](int st, bool acc) {
+          const uint32_t bo = do_mn(st);
 #pragma unroll
-        for (int ks = 0; ks < BQ / 16; ++ks) {
-          // P^T of query columns [16ks, 16ks+16): each elementwise group packs its half over its own S^T columns
-          const int grp = (ks * 16) / (BQ / 2);
-          const uint32_t pa = tm_s + grp * (BQ / 2) + ((ks * 16) % (BQ / 2)) / 2;
-          mma_ts_lo_e(tm_dv, pa, bo + ((ks * 2048) >> 4), idesc_dv, (acc || ks > 0) ? 1u : 0u, el);
-        }
-      };
-      // dK[128 x DH] += dS^T[128 x BQ] (shared memory, K-major) * Q[BQ x DH]
-      auto issue_dk = [&](int st, bool acc) {
-        const uint32_t bq = q_mn(st);
+          for (int ks = 0; ks < BQ / 16; ++ks) {
+            // P^T of query columns [16ks, 16ks+16): each elementwise group packs its half over its own S^T columns
+            const int grp = (ks * 16) / (BQ / 2);
+            const uint32_t pa = tm_s + grp * (BQ / 2) + ((ks * 16) % (BQ / 2)) / 2;
+            mma_ts_lo_e(tm_dv, pa, bo + ((ks * 2048) >> 4), idesc_dv, (acc || ks > 0) ? 1u : 0u, el);
+          }
+        };
+        // dK[128 x DH] += dS^T[128 x BQ] (shared memory, K-major) * Q[BQ x DH]
+        auto issue_dk = [&](int st, bool acc) {
+          const uint32_t bq = q_mn(st);
 #pragma unroll
-        for (int ks = 0; ks < BQ / 16; ++ks)
-          mma_ss_lo_e(tm_dk, ds_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4), bq + ((ks * 2048) >> 4), idesc_dv,
-                      (acc || ks > 0) ? 1u : 0u, el);
-      };
-      // dQ^T[128 (d) x BQ] = K^T[d x 128 (kv)] * dS^T[128 (kv) x BQ]; for head dim 64 the upper 64
-      // rows of the A operand run into the V tile (results in those lanes are ignored).
-      auto issue_dq = [&]() {
+          for (int ks = 0; ks < BQ / 16; ++ks)
+            mma_ss_lo_e(tm_dk, ds_km + (((ks >> 2) * kPanelK + (ks & 3) * 32) >> 4), bq + ((ks * 2048) >> 4), idesc_dv,
+                        (acc || ks > 0) ? 1u : 0u, el);
+        };
+        // dQ^T[128 (d) x BQ] = K^T[d x 128 (kv)] * dS^T[128 (kv) x BQ]; for head dim 64 the upper 64
+        // rows of the A operand run into the V tile (results in those lanes are ignored).
+        auto issue_dq = [&]() {
 #pragma unroll
-        for (int ks = 0; ks < 128 / 16; ++ks)
-          mma_ss_lo_e(tm_dp, k_mn + ((ks * 2048) >> 4), ds_mn + ((ks * 2048) >> 4), idesc_dq, ks > 0 ? 1u : 0u, el);
-      };
+          for (int ks = 0; ks < 128 / 16; ++ks)
+            mma_ss_lo_e(tm_dp, k_mn + ((ks * 2048) >> 4), ds_mn + ((ks * 2048) >> 4), idesc_dq, ks > 0 ? 1u : 0u, el);
+        };
 
-      bool ok = mbar_wait_warp(&bar_kv_full, 0, abort_p);
-      if (ok) ok = mbar_wait_warp(&bar_q_full[0], 0, abort_p);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_s(0);
-        mma_commit_e(&bar_s_full, el);
-        ok = mbar_wait_warp(&bar_do_full[0], 0, abort_p);
-      }
-      if (ok) {
-        tc_fence_after_sync();
-        issue_dp(0);
-        mma_commit_e(&bar_dp_full, el);
-      }
-      for (int t = 0; t < T_total && ok; ++t) {
-        const int st = t % NST;
-        const int st_n = (t + 1) % NST;
-        const uint32_t par_n = ((t + 1) / NST) & 1;
-        const bool more = (t + 1 < T_total);
-        tr.mark(10);
-        if (!mbar_wait_warp(&bar_p_ready, t & 1, abort_p)) break;
-        tr.mark(11);
-        tc_fence_after_sync();
-        issue_dv(st, t > 0);
-        mma_commit_e(&bar_do_empty[st], el);
-        // S^T of the next tile goes out now if its Q tile has landed (a non-blocking probe); otherwise it is the first
-        // thing issued once dS^T is ready.
-        bool s_issued = !more;
-        if (more && __all_sync(0xffffffffu, mbar_test_wait(&bar_q_full[st_n], par_n))) {
-          tr.mark(12);
+        bool ok = mbar_wait_warp(&bar_kv_full, 0, abort_p);
+        if (ok) ok = mbar_wait_warp(&bar_q_full[0], 0, abort_p);
+        if (ok) {
           tc_fence_after_sync();
-          issue_s(st_n);
+          issue_s(0);
           mma_commit_e(&bar_s_full, el);
-          s_issued = true;
+          ok = mbar_wait_warp(&bar_do_full[0], 0, abort_p);
         }
-        tr.mark(13);
-        if (!mbar_wait_warp(&bar_ds_ready, t & 1, abort_p)) break;
-        tr.mark(14);
-        tc_fence_after_sync();
-        if (NST >= 2 && !s_issued) {
-          // The elementwise warps have nothing to do until S^T of the next tile exists: it goes first.  (With a single
-          // Q stage the next tile can only be loaded after dK below has released the slot.)
-          if (!mbar_wait_warp(&bar_q_full[st_n], par_n, abort_p)) break;
+        if (ok) {
           tc_fence_after_sync();
-          issue_s(st_n);
-          mma_commit_e(&bar_s_full, el);
-          s_issued = true;
-        }
-#if RFA_BWD_DK_FIRST
-        issue_dk(st, t > 0);
-        mma_commit_e(&bar_q_empty[st], el);
-        issue_dq();
-        mma_commit_e(&bar_dq_full, el);
-#else
-        issue_dq();
-        mma_commit_e(&bar_dq_full, el);
-        issue_dk(st, t > 0);
-        mma_commit_e(&bar_q_empty[st], el);
-#endif
-        tr.mark(15);
-        if (!s_issued) {
-          if (!mbar_wait_warp(&bar_q_full[st_n], par_n, abort_p)) break;
-          tc_fence_after_sync();
-          issue_s(st_n);
-          mma_commit_e(&bar_s_full, el);
-        }
-        if (more) {
-          if (!mbar_wait_warp(&bar_do_full[st_n], par_n, abort_p)) break;
-          tr.mark(16);
-          if (!mbar_wait_warp(&bar_dq_drained, t & 1, abort_p)) break;
-          tr.mark(17);
-          tc_fence_after_sync();
-          issue_dp(st_n);
+          issue_dp(0);
           mma_commit_e(&bar_dp_full, el);
-          tr.mark(18);
-        } else {
-          mma_commit_e(&bar_final, el);
+        }
+        for (int t = 0; t < T_total && ok; ++t) {
+          const int st = t % NST;
+          const int st_n = (t + 1) % NST;
+          const uint32_t par_n = ((t + 1) / NST) & 1;
+          const bool more = (t + 1 < T_total);
+          tr.mark(10);
+          if (!mbar_wait_warp(&bar_p_ready, t & 1, abort_p)) break;
+          tr.mark(11);
+          tc_fence_after_sync();
+          issue_dv(st, t > 0);
+          mma_commit_e(&bar_do_empty[st], el);
+          // S^T of the next tile goes out now if its Q tile has landed (a non-blocking probe); otherwise it is the
+          // first thing issued once dS^T is ready.
+          bool s_issued = !more;
+          if (more && __all_sync(0xffffffffu, mbar_test_wait(&bar_q_full[st_n], par_n))) {
+            tr.mark(12);
+            tc_fence_after_sync();
+            issue_s(st_n);
+            mma_commit_e(&bar_s_full, el);
+            s_issued = true;
+          }
+          tr.mark(13);
+          if (!mbar_wait_warp(&bar_ds_ready, t & 1, abort_p)) break;
+          tr.mark(14);
+          tc_fence_after_sync();
+          if (NST >= 2 && !s_issued) {
+            // The elementwise warps have nothing to do until S^T of the next tile exists: it goes first.  (With a
+            // single Q stage the next tile can only be loaded after dK below has released the slot.)
+            if (!mbar_wait_warp(&bar_q_full[st_n], par_n, abort_p)) break;
+            tc_fence_after_sync();
+            issue_s(st_n);
+            mma_commit_e(&bar_s_full, el);
+            s_issued = true;
+          }
+#if RFA_BWD_DK_FIRST
+          issue_dk(st, t > 0);
+          mma_commit_e(&bar_q_empty[st], el);
+          issue_dq();
+          mma_commit_e(&bar_dq_full, el);
+#else
+          issue_dq();
+          mma_commit_e(&bar_dq_full, el);
+          issue_dk(st, t > 0);
+          mma_commit_e(&bar_q_empty[st], el);
+#endif
+          tr.mark(15);
+          if (!s_issued) {
+            if (!mbar_wait_warp(&bar_q_full[st_n], par_n, abort_p)) break;
+            tc_fence_after_sync();
+            issue_s(st_n);
+            mma_commit_e(&bar_s_full, el);
+          }
+          if (more) {
+            if (!mbar_wait_warp(&bar_do_full[st_n], par_n, abort_p)) break;
+            tr.mark(16);
+            if (!mbar_wait_warp(&bar_dq_drained, t & 1, abort_p)) break;
+            tr.mark(17);
+            tc_fence_after_sync();
+            issue_dp(st_n);
+            mma_commit_e(&bar_dp_full, el);
+            tr.mark(18);
+          } else {
+            mma_commit_e(&bar_final, el);
+          }
         }
       }
+      __syncwarp();
     }
-    __syncwarp();
-   }
   } else if (warp < 12) {
     // =========================== elementwise warpgroups ===========================
     // Two warpgroups share every tile: group cw owns query columns [cw*BQ/2, (cw+1)*BQ/2).
