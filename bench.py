@@ -426,7 +426,7 @@ def main():
             "peak_used_for_step": {"bf16_tflops_sustained": peak_sus, "kind": peak_kind},
             "roofline": {"bound": "tensor", "kernel": "bwd_hop_kernel (diagonal block)", "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_kind": peak_kind + " burst",
-                         "traffic": (1634403064 if args.config == "c3" else None),
+                         "traffic": (998444544 if args.config == "c3" else None),
                          "traffic_note": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch (profiles/bwd_hop_kernel_c3_diag.md)",
                          "ms_per_launch": bwd_ms,
                          "fwd_hop": {"achieved": fwd_flops / (fwd_ms * 1e-3) / 1e12, "ms_per_launch": fwd_ms,
