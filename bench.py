@@ -217,6 +217,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="capture the step (forward + backward) into a CUDA graph and time replays (1 GPU only)")
     ap.add_argument("--zigzag", action="store_true",
                     help="zigzag layout (rank r holds chunks r and 2W-1-r): balanced causal work; not the headline config")
     args = ap.parse_args()
@@ -253,6 +255,25 @@ def main():
         out.backward(dout)
         return out
 
+    if args.graph:
+        if world > 1:
+            raise SystemExit("--graph is measured on one GPU only")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):  # workspaces and function attributes are set up outside the capture
+            for _ in range(2):
+                step_device()
+        torch.cuda.current_stream().wait_stream(side)
+        qg.grad = kg.grad = vg.grad = None
+        cuda_graph = torch.cuda.CUDAGraph()
+        launches_c0 = _native.launch_count()
+        with torch.cuda.graph(cuda_graph):
+            ring_flash_attn(qg, kg, vg, softmax_scale=scale, causal=True, zigzag=args.zigzag).backward(dout)
+        launches_per_replay = _native.launch_count() - launches_c0
+
+        def step_device():  # noqa: F811 - the timed step is now one graph launch
+            cuda_graph.replay()
+
     flush = None
     bytes_resident = sum(x.numel() * x.element_size() for x in (q, k, v, dout)) * 2 + q.numel() * 4
     if bytes_resident < 2 * 126 * 2 ** 20:
@@ -281,6 +302,8 @@ def main():
         ev[i][1].record()
     barrier()
     launches = _native.launch_count() - launches0
+    if args.graph:
+        launches = launches_per_replay * args.steps  # the kernels run from the graph, not through the C ABI
     ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -417,7 +440,8 @@ def main():
             "warmup": warmup, "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"{args.config}: {desc}, causal, fwd+bwd, world size {W}"
-                                   + (", zigzag layout" if args.zigzag else ", contiguous shards"),
+                                   + (", zigzag layout" if args.zigzag else ", contiguous shards")
+                                   + (", step replayed from a CUDA graph" if args.graph else ""),
                        "l2": "L2 flushed (256 MiB write) between timed steps" if flush is not None
                              else "per-step inputs+outputs exceed the 126 MB L2",
                        "flops": "algorithmic causal FLOPs: 3.5*(W^2/2)*4*B*Hq*S_local^2*D for the job"},
