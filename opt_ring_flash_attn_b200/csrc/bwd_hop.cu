@@ -626,6 +626,13 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
+    // The kernel trades registers between its warpgroups inside the pool the launch allocates (threads x registers
+    // per thread); a raise that the pool cannot satisfy would wait forever, so a build whose register count does not
+    // cover the allowances is refused here instead of launched.
+    cudaFuncAttributes fa;
+    e = cudaFuncGetAttributes(&fa, kern);
+    if (e != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
+    if (fa.numRegs * Cfg::kThreads < 128 * 64 + 256 * 128 + 256 * 80) return RFA_ERR_UNSUPPORTED;
     attr_done = true;
   }
   BwdParams pr = prm;
