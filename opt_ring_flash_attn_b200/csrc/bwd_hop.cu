@@ -34,6 +34,8 @@
 // the 64 KB of dQ^T of a tile need >= 2048 cycles whatever issues them; unpaced, the eight reduction warps keep the
 // load/store queue full of reductions and every shared-memory or tensor-memory access of the elementwise warps
 // waits behind them.
+// Every n-th group of four exponentials of the P^T phase on the FMA pipe (0 = all on the special-function unit, which
+// measured best here: the phase is bound by shared-memory and load/store traffic, not by exp2).
 #ifndef RFA_BWD_POLY_EVERY
 #define RFA_BWD_POLY_EVERY 0
 #endif
@@ -577,6 +579,7 @@ __global__ void __launch_bounds__(640, 1)
       mbar_arrive(&bar_dq_drained);
       tr.mark(31);
 #ifdef RFA_DIAG_NO_RED
+      // Timing diagnostic only (dQ comes out wrong): shows what the reductions cost the rest of the kernel.
       if (false) {
 #else
       if (d_ok) {
