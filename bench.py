@@ -419,7 +419,7 @@ def main():
         e2e_ms = min(e2e_passes)
         h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv, hdo))
         d2h = sum(x.numel() * x.element_size() for x in (h_out, h_dq, h_dk, h_dv))
-    for ws in list(workspace._fwd_cache.values()) + list(workspace._bwd_cache.values()):
+    for ws in workspace.all_workspaces():
         _native.check_status(ws.status, "bench")
 
     if rank == 0:

@@ -10,8 +10,11 @@
  *
  * Rules of the ABI
  *  - plain pointers and sizes only; all pointers are device pointers unless
- *    stated otherwise; the library allocates nothing and keeps no pointer
- *    after a call returns;
+ *    stated otherwise; the compute entry points allocate nothing and keep no
+ *    pointer after a call returns (the transport handle of rfa_comm_init owns a
+ *    communicator, a stream and a few events until rfa_comm_destroy);
+ *  - the device the stream belongs to must be the current device of the calling
+ *    thread;
  *  - every call is asynchronous on `stream` (a cudaStream_t passed as void*);
  *    no call synchronises the device;
  *  - return value: RFA_OK or a negative RFA_ERR_* code (never an exception,
@@ -124,13 +127,30 @@ int rfa_bwd_hop(const void* q, const void* k, const void* v, const void* dout, c
 /*
  * rfa_bwd_hop restricted to a window, for the zigzag layout (`_zigzag_backward`,
  * optimized_ring_flash_attn.py:1198-1275): only query rows >= q_begin contribute and only keys < kv_len are
- * processed; rows of dkdv_out at or beyond kv_len receive the previous partial sums (accumulate_prev) or zero.
+ * processed (kv_len need not be a multiple of the 128-row tile: keys at or beyond it inside the last tile are masked
+ * out of P, so they add nothing to dQ); rows of dkdv_out at or beyond kv_len receive the previous partial sums
+ * (accumulate_prev) or zero.
  * rfa_bwd_hop(...) == rfa_bwd_hop_window(..., q_begin=0, kv_len=Skv).
  */
 int rfa_bwd_hop_window(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
                        const float* delta, float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B, int Sq,
                        int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale, int accumulate_prev,
                        int causal_diag, int q_begin, int kv_len, int* status, void* stream);
+
+/*
+ * rfa_bwd_hop_window with bit-reproducible dQ: the contributions of the K/V tiles to a dQ accumulator tile are
+ * added in K/V-tile order (a counter per accumulator tile; each CTA waits, bounded, for the tiles before it), and
+ * a GQA group is never split over CTAs.  This restores what the reference's dQ kernel has by construction (it owns
+ * its tile and updates it with a plain read-modify-write, optimized_ring_flash_attn.py:730-735) and is what
+ * `deterministic=True` of the baseline-style wrappers (ring_flash_attn.py:179, 245) selects.  Slower than the
+ * unordered hop (CTAs of neighbouring K/V tiles run one query tile apart).
+ *  dq_order  int32 [rfa_dq_order_elems(B,Sq,Hq,D)] scratch, cleared by the call itself.
+ */
+size_t rfa_dq_order_elems(int B, int Sq, int Hq, int D);
+int rfa_bwd_hop_ordered(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
+                        const float* delta, float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B, int Sq,
+                        int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale, int accumulate_prev,
+                        int causal_diag, int q_begin, int kv_len, int* dq_order, int* status, void* stream);
 
 /*
  * out[i] = prev[i] + block[i] for n fp32 elements (n % 4 == 0; out may alias prev or block).
@@ -167,6 +187,8 @@ int rfa_dkdv_accumulate_to16(const void* prev, const float* block, void* out, si
  *    that device current); make that first call before any stream capture begins.
  *  - All calls on a device share the one array: it is cleared at the start of every call, and two
  *    calls that overlap on the GPU (different streams) race on it -- issue them on one stream.
+ *  - The array is chosen by the calling thread's current device, which must be the stream's device.
+ *  - Every argument is checked before anything is enqueued: a refused call leaves the stream untouched.
  */
 #define RFA_NOALLOC_SCRATCH_BYTES (32u * 1024u * 1024u)
 size_t rfa_noalloc_scratch_bytes(void);
@@ -207,31 +229,16 @@ int rfa_pack_kv(const void* k, const void* v, void* dst, size_t bytes_each, void
  *        (or a negative error).  Asynchronous.  send and recv must differ.
  *  rfa_ring_wait(handle, slot, compute_stream)   compute_stream waits for that transfer; the host does not.
  *  rfa_comm_destroy(handle)
- * At most 8 posts may be outstanding (not yet waited for) per handle.  Host pointers: out128, id, handle.
+ * At most 8 posts may be outstanding (not yet waited for) per handle; a ninth is refused with
+ * RFA_ERR_INVALID_ARG, as is a wait with nothing outstanding.  The handle's stream has the highest stream priority
+ * of the device, so that the transfer's blocks are scheduled ahead of pending blocks of a running hop kernel.
+ * Host pointers: out128, id, handle.
  */
 int rfa_comm_unique_id(void* out128);
 int rfa_comm_init(const void* id128, int rank, int world, void** handle);
 int rfa_comm_destroy(void* handle);
 int rfa_ring_post(void* handle, const void* send, void* recv, size_t bytes, void* compute_stream);
 int rfa_ring_wait(void* handle, int slot, void* compute_stream);
-
-/*
- * Diagnostic: one 128x128x128 tensor-core product through each operand path the
- * hop kernels use (mode 0..4), C fp32 [128,128] row-major, A and B bf16
- * [128,128] row-major.  Modes: 0 C=A*B^T (both K-major, shared memory);
- * 1 C=A*B (B MN-major); 2 C=A*B with A staged in tensor memory; 3 C=A^T*B (both
- * MN-major); 4 as 0 with A written to shared memory by threads.
- * No counterpart in the reference.
- */
-int rfa_debug_mma_probe(int mode, const void* a, const void* b, float* c, int* status, void* stream);
-
-/*
- * Diagnostic: when `buf` is non-NULL, the hop kernels launched afterwards record per-role pipeline
- * events of their first `n_ctas` CTAs into buf, laid out [n_ctas][5 roles][cap] 64-bit words
- * (tag << 48 | SM clock; roles: 0 loader, 1 MMA issuer, 2/3 elementwise groups, 4 dQ reduction).
- * NULL switches tracing off.  Host-side state; not thread safe.  No counterpart in the reference.
- */
-int rfa_debug_set_trace(unsigned long long* buf, int n_ctas, int cap);
 
 #ifdef __cplusplus
 }

@@ -6,14 +6,45 @@ reference's entry point (optimized_ring_flash_attn.py:1297-1367): forward saves
 """
 from __future__ import annotations
 
+import contextlib
+import os
+import threading
 from typing import Optional, Tuple
 
 import torch
 import torch.distributed as dist
 
-from . import schedule
+from . import schedule, workspace
 
 _SUPPORTED = (torch.bfloat16, torch.float16)
+
+_mode = threading.local()
+
+
+def _deterministic_now() -> bool:
+    v = getattr(_mode, "deterministic", None)
+    return (os.environ.get("RFA_B200_DETERMINISTIC", "0") == "1") if v is None else bool(v)
+
+
+@contextlib.contextmanager
+def deterministic(enabled: bool = True):
+    """Calls of :func:`ring_flash_attn` made inside this context compute bit-reproducible gradients: the dQ
+    contributions of the K/V tiles are added in a fixed order instead of by unordered fp32 reductions (the
+    reference's dQ kernel is deterministic by construction, optimized_ring_flash_attn.py:730-735).  The choice is
+    taken at forward time and holds for that call's backward.  ``RFA_B200_DETERMINISTIC=1`` sets the default."""
+    prev = getattr(_mode, "deterministic", None)
+    _mode.deterministic = enabled
+    try:
+        yield
+    finally:
+        _mode.deterministic = prev
+
+
+def check(what: str = "ring_flash_attn") -> None:
+    """Synchronise and raise ``RuntimeError`` if a kernel of any earlier call reported a failure through its device
+    status word (a bounded pipeline wait that ran out).  Without this call such a failure surfaces at the start
+    of the next forward or backward that uses the same scratch; ``RFA_B200_SYNC_STATUS=1`` checks after every pass."""
+    workspace.check_all(what)
 
 
 def _validate(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float) -> None:
@@ -54,6 +85,7 @@ class _RingFlashAttnFunc(torch.autograd.Function):
         ctx.softmax_scale = softmax_scale
         ctx.causal = causal
         ctx.group = group
+        ctx.deterministic = _deterministic_now()
         ctx.mark_non_differentiable(lse)
         return out, lse
 
@@ -61,9 +93,11 @@ class _RingFlashAttnFunc(torch.autograd.Function):
     def backward(ctx, dout, _dlse=None):
         q, k, v, out, lse = ctx.saved_tensors
         if ctx.zigzag:
-            dq, dk, dv = schedule.zigzag_backward(ctx.group, dout, q, k, v, out, lse, ctx.softmax_scale)
+            dq, dk, dv = schedule.zigzag_backward(ctx.group, dout, q, k, v, out, lse, ctx.softmax_scale,
+                                                  deterministic=ctx.deterministic)
         else:
-            dq, dk, dv = schedule.ring_backward(ctx.group, dout, q, k, v, out, lse, ctx.softmax_scale, ctx.causal)
+            dq, dk, dv = schedule.ring_backward(ctx.group, dout, q, k, v, out, lse, ctx.softmax_scale, ctx.causal,
+                                                deterministic=ctx.deterministic)
         return dq, dk, dv, None, None, None, None
 
 

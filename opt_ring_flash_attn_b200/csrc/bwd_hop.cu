@@ -22,32 +22,24 @@
 // query columns each).
 // Tensor memory: [0,BQ) S^T / P^T, [BQ,2BQ) dP^T then dQ^T, then dV (DH) and dK (DH).
 // Head dim 256 runs as two CTAs per tile, each owning 128 columns of dK, dV, dQ.
-#include <stdlib.h>
-
 #include <type_traits>
 
 #include "bwd_common.cuh"
 #include "common.h"
 #include "tc05.cuh"
 
+namespace rfa {
+
 // Pause (ns) a reduction warp takes after each vector reduction.  An SM can push 32 B per clock towards the L2, so
 // the 64 KB of dQ^T of a tile need >= 2048 cycles whatever issues them; unpaced, the eight reduction warps keep the
 // load/store queue full of reductions and every shared-memory or tensor-memory access of the elementwise warps
 // waits behind them.
+constexpr unsigned kRedSleepNs = 100;
 // Every n-th group of four exponentials of the P^T phase on the FMA pipe (0 = all on the special-function unit, which
 // measured best here: the phase is bound by shared-memory and load/store traffic, not by exp2).
-#ifndef RFA_BWD_POLY_EVERY
-#define RFA_BWD_POLY_EVERY 0
-#endif
-// After dS^T is ready: dK before dQ^T (1) or after it (0).  dK first releases the Q slot ~500 cycles earlier, which
-// matters more than the reduction starting earlier: a Q tile load takes 1500-3000 cycles under the L2 load of the
-// reductions and only two Q stages fit in shared memory.
-#ifndef RFA_BWD_DK_FIRST
-#define RFA_BWD_DK_FIRST 1
-#endif
-#ifndef RFA_RED_SLEEP
-#define RFA_RED_SLEEP 100
-#endif
+constexpr int kBwdPolyEvery = 0;
+
+}  // namespace rfa
 
 namespace rfa {
 
@@ -329,17 +321,13 @@ __global__ void __launch_bounds__(640, 1)
             mma_commit_e(&bar_s_full, el);
             s_issued = true;
           }
-#if RFA_BWD_DK_FIRST
+          // dK before dQ^T: it releases the Q slot ~500 cycles earlier, which matters more than the reduction
+          // starting earlier (a Q tile load takes 1500-3000 cycles under the L2 load of the reductions and only two
+          // Q stages fit in shared memory).
           issue_dk(st, t > 0);
           mma_commit_e(&bar_q_empty[st], el);
           issue_dq();
           mma_commit_e(&bar_dq_full, el);
-#else
-          issue_dq();
-          mma_commit_e(&bar_dq_full, el);
-          issue_dk(st, t > 0);
-          mma_commit_e(&bar_q_empty[st], el);
-#endif
           tr.mark(15);
           if (!s_issued) {
             if (!mbar_wait_warp(&bar_q_full[st_n], par_n, abort_p)) break;
@@ -373,11 +361,15 @@ __global__ void __launch_bounds__(640, 1)
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // kv row inside the tile
     const int kvpos = n0 + row;
+    // Queries before mask_lim get P = 0 for this key: the causal rule on a diagonal block (query before key), and every
+    // query when the key lies at or beyond kv_len (a window that ends inside this tile: those keys are real rows of the
+    // K/V tensors, so without the mask they would add to dQ).
+    const int mask_lim = (kvpos >= p.kv_len) ? 0x7fffffff : (p.causal ? kvpos : static_cast<int>(0x80000000));
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const int col0 = cw * kHalfCols;
     const uint32_t a_s = tmem_base + lane_addr + Cfg::kTmS + col0;
     const uint32_t a_dp = tmem_base + lane_addr + Cfg::kTmDP + col0;
-    constexpr int kPolyEvery = RFA_BWD_POLY_EVERY;  // of the 8 groups of four exponentials per 32 columns
+    constexpr int kPolyEvery = kBwdPolyEvery;  // of the 8 groups of four exponentials per 32 columns
     const Exp2Poly exp2_poly;
     const uint64_t nscale2 = pack_f2(-p.scale_log2, -p.scale_log2);
     bool ok = run;
@@ -392,7 +384,7 @@ __global__ void __launch_bounds__(640, 1)
       tr.mark(20);
       tc_fence_after_sync();
       const int q0 = i * BQ + col0;
-      const bool masked = p.causal && (i * BQ < n0 + 127);
+      const bool masked = (p.causal && (i * BQ < n0 + 127)) || (n0 + 128 > p.kv_len);
       uint32_t pk[NCH * 16];
       {
         uint32_t r[NCH][32];
@@ -402,7 +394,7 @@ __global__ void __launch_bounds__(640, 1)
 #pragma unroll
         for (int c = 1; c < NCH; ++c) reg_fence32(r[c]);
         tr.mark(21);
-        // P^T = exp2(scale*log2e * S^T - lse2[q]); the causal mask (query before key) only on diagonal tiles.
+        // P^T = exp2(scale*log2e * S^T - lse2[q]); masked only on diagonal tiles and on a tile that straddles kv_len.
         // Packed pairs: y = lse2 - c*s in one fma, then 2^(-y); every kPolyEvery-th pair on the FMA pipe.
         auto p_phase = [&](auto mask_tag) {
           constexpr bool kMask = decltype(mask_tag)::value;
@@ -428,10 +420,10 @@ __global__ void __launch_bounds__(640, 1)
               }
               if (kMask) {
                 const int qp = q0 + c * 32 + k * 4;
-                if (qp + 0 < kvpos) e0 = 0.f;
-                if (qp + 1 < kvpos) e1 = 0.f;
-                if (qp + 2 < kvpos) e2 = 0.f;
-                if (qp + 3 < kvpos) e3 = 0.f;
+                if (qp + 0 < mask_lim) e0 = 0.f;
+                if (qp + 1 < mask_lim) e1 = 0.f;
+                if (qp + 2 < mask_lim) e2 = 0.f;
+                if (qp + 3 < mask_lim) e3 = 0.f;
               }
               pk[c * 16 + 2 * k + 0] = Pack2<T>::pack(e0, e1);
               pk[c * 16 + 2 * k + 1] = Pack2<T>::pack(e2, e3);
@@ -578,12 +570,30 @@ __global__ void __launch_bounds__(640, 1)
       tc_fence_before_sync();
       mbar_arrive(&bar_dq_drained);
       tr.mark(31);
-#ifdef RFA_DIAG_NO_RED
-      // Timing diagnostic only (dQ comes out wrong): shows what the reductions cost the rest of the kernel.
-      if (false) {
-#else
+      // Ordered mode (bit-reproducible dQ): the contributions of the kv tiles to one accumulator tile are added in
+      // kv-tile order.  One counter per (head, query tile, warp slice); the CTA of kv tile j adds after j earlier
+      // tiles have.  CTAs are numbered kv tile first, so the CTA waited for was dispatched before this one: it is
+      // resident or finished, never pending behind the waiter.
+      int* order_sem = nullptr;
+      if (p.dq_order != nullptr) {
+        order_sem = p.dq_order +
+                    ((((static_cast<size_t>(b) * p.Hq + hq) * nQtiles + q_tile(t)) * Cfg::kHalves + hf) * 2 + half) * 4 +
+                    quarter;
+        bool got = true;
+        if (lane == 0 && d_ok) {
+          const unsigned long long t0 = global_timer_ns();
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(order_sem) < kvt) {
+            if (((++spins) & 0x3fu) == 0) {
+              if (*abort_p) { got = false; break; }
+              if (global_timer_ns() - t0 > kWaitLimitNs) { *abort_p = 1; got = false; break; }
+            }
+            __nanosleep(64);
+          }
+        }
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+      }
       if (d_ok) {
-#endif
         // rows beyond Sq and head-dim columns beyond D hold exact zeros (zero-filled operands, P = 0)
 #pragma unroll
         for (int c = 0; c < NCR; ++c) {
@@ -592,8 +602,13 @@ __global__ void __launch_bounds__(640, 1)
             red_add_v4_f32(base + static_cast<size_t>(c * 8 + k) * DP * 4, __uint_as_float(r[c][4 * k + 0]) * p.scale,
                            __uint_as_float(r[c][4 * k + 1]) * p.scale, __uint_as_float(r[c][4 * k + 2]) * p.scale,
                            __uint_as_float(r[c][4 * k + 3]) * p.scale);
-            if (RFA_RED_SLEEP > 0) __nanosleep(RFA_RED_SLEEP);
+            if (kRedSleepNs > 0) __nanosleep(kRedSleepNs);
           }
+        }
+        if (order_sem != nullptr) {
+          __threadfence();  // this lane's reductions are performed before the counter moves
+          __syncwarp();
+          if (lane == 0) red_release_gpu_add(order_sem, 1);
         }
       }
     }
@@ -625,8 +640,11 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   if ((rc = make_tmap_bshd(&tk, k, dtype, prm.B, prm.Skv, prm.Hkv, prm.D, 128)) != RFA_OK) return rc;
   if ((rc = make_tmap_bshd(&tv, v, dtype, prm.B, prm.Skv, prm.Hkv, prm.D, 128)) != RFA_OK) return rc;
   auto kern = bwd_hop_kernel<DP, DH, BQ, NST, T>;
-  static bool attr_done = false;
-  if (!attr_done) {
+  // Function attributes belong to a device: the opt-in to large dynamic shared memory is made once per device.
+  static bool attr_done[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return RFA_ERR_CUDA; }
+  if (!attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
     // The kernel trades registers between its warpgroups inside the pool the launch allocates (threads x registers
@@ -636,13 +654,17 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
     e = cudaFuncGetAttributes(&fa, kern);
     if (e != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
     if (fa.numRegs * Cfg::kThreads < 128 * 64 + 256 * 128 + 256 * 80) return RFA_ERR_UNSUPPORTED;
-    attr_done = true;
+    attr_done[dev] = true;
   }
   BwdParams pr = prm;
   const long long base_units = static_cast<long long>(ceil_div(prm.kv_len, 128)) * prm.Hkv * prm.B * Cfg::kHalves;
   {
     const int rc2 = choose_group_split(pr, base_units, stream);
     if (rc2 != RFA_OK) return rc2;
+  }
+  if (pr.dq_order != nullptr) {
+    const size_t n = static_cast<size_t>(prm.B) * prm.Hq * ceil_div(prm.Sq, BQ) * Cfg::kHalves * 8;
+    if (cudaMemsetAsync(pr.dq_order, 0, n * sizeof(int), stream) != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
   }
   const unsigned grid = static_cast<unsigned>(base_units * pr.gsplit);
   kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, tdo, pr);
@@ -662,24 +684,47 @@ static int dispatch_bwd(int dp, const void* q, const void* k, const void* v, con
 
 }  // namespace rfa
 
-extern "C" int rfa_bwd_hop_window(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
-                                  const float* delta, float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B,
-                                  int Sq, int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale,
-                                  int accumulate_prev, int causal_diag, int q_begin, int kv_len, int* status,
-                                  void* stream) {
-  using namespace rfa;
-  if (!q || !k || !v || !dout || !lse2 || !delta || !dq_acc || !dkdv_out || !status) return RFA_ERR_INVALID_ARG;
+// Argument checks shared by every backward-hop entry point (nothing is enqueued before they pass).
+int rfa::bwd_check_args(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
+                        const float* delta, const float* dkdv_prev, const float* dkdv_out, int B, int Sq, int Skv,
+                        int Hq, int Hkv, int D, int dtype, float softmax_scale, int accumulate_prev, int causal_diag,
+                        int q_begin, int kv_len, const int* status) {
+  if (!q || !k || !v || !dout || !lse2 || !delta || !dkdv_out || !status) return RFA_ERR_INVALID_ARG;
   if (accumulate_prev && !dkdv_prev) return RFA_ERR_INVALID_ARG;
   if (B <= 0 || Sq <= 0 || Skv <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0) return RFA_ERR_INVALID_ARG;
   if (!(softmax_scale > 0.f)) return RFA_ERR_INVALID_ARG;
   if (causal_diag && Sq != Skv) return RFA_ERR_INVALID_ARG;
   if (q_begin < 0 || q_begin >= Sq || (q_begin % 128) != 0 || kv_len <= 0 || kv_len > Skv) return RFA_ERR_INVALID_ARG;
-  const int dp = padded_head_dim(D);
-  if (dp == 0) return RFA_ERR_UNSUPPORTED;
+  if (padded_head_dim(D) == 0) return RFA_ERR_UNSUPPORTED;
   if (dtype != RFA_DTYPE_BF16 && dtype != RFA_DTYPE_FP16) return RFA_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(lse2) & 15u) || (reinterpret_cast<uintptr_t>(delta) & 15u) ||
       (reinterpret_cast<uintptr_t>(dkdv_out) & 15u) || (reinterpret_cast<uintptr_t>(dkdv_prev) & 15u))
     return RFA_ERR_INVALID_ARG;
+  return RFA_OK;
+}
+
+// Query-tile width of the backward kernel for a padded head dim (the granularity of the ordering counters).
+static int bwd_q_tile(int dp) { return dp == 256 ? 64 : 128; }
+
+extern "C" size_t rfa_dq_order_elems(int B, int Sq, int Hq, int D) {
+  const int dp = rfa::padded_head_dim(D);
+  if (dp == 0 || B <= 0 || Sq <= 0 || Hq <= 0) return 0;
+  return static_cast<size_t>(B) * Hq * rfa::ceil_div(Sq, bwd_q_tile(dp)) * (dp == 256 ? 2 : 1) * 8;
+}
+
+static int bwd_hop_impl(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
+                        const float* delta, float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B, int Sq,
+                        int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale, int accumulate_prev,
+                        int causal_diag, int q_begin, int kv_len, int* dq_order, int* status, void* stream) {
+  using namespace rfa;
+  if (!dq_acc) return RFA_ERR_INVALID_ARG;
+  {
+    const int rc = bwd_check_args(q, k, v, dout, lse2, delta, dkdv_prev, dkdv_out, B, Sq, Skv, Hq, Hkv, D, dtype,
+                                  softmax_scale, accumulate_prev, causal_diag, q_begin, kv_len, status);
+    if (rc != RFA_OK) return rc;
+  }
+  if (reinterpret_cast<uintptr_t>(dq_order) & 3u) return RFA_ERR_INVALID_ARG;
+  const int dp = padded_head_dim(D);
   BwdParams prm;
   prm.lse2 = lse2;
   prm.delta = delta;
@@ -701,6 +746,7 @@ extern "C" int rfa_bwd_hop_window(const void* q, const void* k, const void* v, c
   prm.kv_len = kv_len;
   prm.gsplit = 1;
   prm.reduce_out = 0;
+  prm.dq_order = dq_order;
   prm.status = status;
   prm.trace = g_trace.buf;
   prm.trace_ctas = g_trace.ctas;
@@ -710,10 +756,30 @@ extern "C" int rfa_bwd_hop_window(const void* q, const void* k, const void* v, c
   return dispatch_bwd<__half>(dp, q, k, v, dout, prm, dtype, s);
 }
 
+extern "C" int rfa_bwd_hop_window(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
+                                  const float* delta, float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B,
+                                  int Sq, int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale,
+                                  int accumulate_prev, int causal_diag, int q_begin, int kv_len, int* status,
+                                  void* stream) {
+  return bwd_hop_impl(q, k, v, dout, lse2, delta, dq_acc, dkdv_prev, dkdv_out, B, Sq, Skv, Hq, Hkv, D, dtype,
+                      softmax_scale, accumulate_prev, causal_diag, q_begin, kv_len, /*dq_order=*/nullptr, status, stream);
+}
+
+extern "C" int rfa_bwd_hop_ordered(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
+                                   const float* delta, float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B,
+                                   int Sq, int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale,
+                                   int accumulate_prev, int causal_diag, int q_begin, int kv_len, int* dq_order,
+                                   int* status, void* stream) {
+  if (!dq_order) return RFA_ERR_INVALID_ARG;
+  return bwd_hop_impl(q, k, v, dout, lse2, delta, dq_acc, dkdv_prev, dkdv_out, B, Sq, Skv, Hq, Hkv, D, dtype,
+                      softmax_scale, accumulate_prev, causal_diag, q_begin, kv_len, dq_order, status, stream);
+}
+
 extern "C" int rfa_bwd_hop(const void* q, const void* k, const void* v, const void* dout, const float* lse2,
                            const float* delta, float* dq_acc, const float* dkdv_prev, float* dkdv_out, int B, int Sq,
                            int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale, int accumulate_prev,
                            int causal_diag, int* status, void* stream) {
-  return rfa_bwd_hop_window(q, k, v, dout, lse2, delta, dq_acc, dkdv_prev, dkdv_out, B, Sq, Skv, Hq, Hkv, D, dtype,
-                            softmax_scale, accumulate_prev, causal_diag, /*q_begin=*/0, /*kv_len=*/Skv, status, stream);
+  return bwd_hop_impl(q, k, v, dout, lse2, delta, dq_acc, dkdv_prev, dkdv_out, B, Sq, Skv, Hq, Hkv, D, dtype,
+                      softmax_scale, accumulate_prev, causal_diag, /*q_begin=*/0, /*kv_len=*/Skv, /*dq_order=*/nullptr,
+                      status, stream);
 }

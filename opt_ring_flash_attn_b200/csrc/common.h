@@ -7,8 +7,12 @@
 #include <stdint.h>
 
 #include "../../include/rfa_b200.h"
+#include "../../include/rfa_b200_debug.h"
 
 namespace rfa {
+
+// Per-device launcher state (function attributes, scratch addresses) is kept in arrays of this size.
+constexpr int kMaxDevices = 64;
 
 inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 inline int ceil_div(int x, int m) { return (x + m - 1) / m; }

@@ -19,11 +19,11 @@
 #include "common.h"
 #include "tc05.cuh"
 
-#ifndef RFA_FWD_POLY_EVERY
-#define RFA_FWD_POLY_EVERY 4
-#endif
-
 namespace rfa {
+
+// Every n-th pair of exponentials of the softmax on the FMA pipe (a cubic) instead of the special-function unit,
+// which needs as many cycles per K/V tile as the tensor pipe does; 4 measured best (0 = none).
+constexpr int kFwdPolyEvery = 4;
 
 struct FwdParams {
   float* acc;
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(128 + NQ * 128, 1)
   __shared__ uint64_t bar_kv_empty[kSlots];
   __shared__ uint64_t bar_s_full[NQ * NS];
   constexpr int kPvParts = BN / 32;  // one hand-off per 32 keys
-  constexpr int kPolyEvery = RFA_FWD_POLY_EVERY;  // every n-th pair of exponentials on the FMA pipe (0 = none)
+  constexpr int kPolyEvery = kFwdPolyEvery;  // every n-th pair of exponentials on the FMA pipe (0 = none)
   __shared__ uint64_t bar_p_ready[NQ * NS * kPvParts];  // [score buffer][part of the keys]
   __shared__ uint64_t bar_pv_done[NQ];
   __shared__ uint32_t tmem_holder;
@@ -540,11 +540,14 @@ static int launch_fwd(const void* q, const void* k, const void* v, const FwdPara
   if ((rc = make_tmap_bshd(&tk, k, dtype, prm.B, prm.Skv, prm.Hkv, prm.D, BN)) != RFA_OK) return rc;
   if ((rc = make_tmap_bshd(&tv, v, dtype, prm.B, prm.Skv, prm.Hkv, prm.D, BN)) != RFA_OK) return rc;
   auto kern = fwd_hop_kernel<DP, BN, NQ, NS, T>;
-  static bool attr_done = false;  // per instantiation
-  if (!attr_done) {
+  // Function attributes belong to a device: one flag per instantiation and device.
+  static bool attr_done[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return RFA_ERR_CUDA; }
+  if (!attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) { cudaGetLastError(); return RFA_ERR_CUDA; }
-    attr_done = true;
+    attr_done[dev] = true;
   }
   const int nQs = (prm.nQt - prm.q_begin / 128 + NQ - 1) / NQ;
   const unsigned grid = static_cast<unsigned>(nQs) * prm.Hq * prm.B;

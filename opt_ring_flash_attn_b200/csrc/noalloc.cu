@@ -11,6 +11,7 @@
 // RFA_NOALLOC_SCRATCH_BYTES of it until the process exits, which is why the limit is modest.
 // In host code the array's name is only a handle; the device address is looked up once per device
 // with cudaGetSymbolAddress (with that device current) and passed to the kernels as a pointer.
+#include "bwd_common.cuh"
 #include "common.h"
 
 namespace {
@@ -18,13 +19,12 @@ namespace {
 constexpr size_t kScratchBytes = RFA_NOALLOC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kScratchBytes];
 
-constexpr int kMaxDevices = 64;
-float* g_scratch_ptr[kMaxDevices] = {nullptr};
+float* g_scratch_ptr[rfa::kMaxDevices] = {nullptr};
 
 // Device address of the scratch array on the current device (looked up on first use).
 int scratch_for_current_device(float** out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= rfa::kMaxDevices) {
     cudaGetLastError();
     return RFA_ERR_CUDA;
   }
@@ -48,7 +48,14 @@ extern "C" int rfa_bwd_hop_noalloc(const void* q, const void* k, const void* v, 
                                    const float* delta, void* dq, const float* dkdv_prev, float* dkdv_out, int B,
                                    int Sq, int Skv, int Hq, int Hkv, int D, int dtype, float softmax_scale,
                                    int accumulate_prev, int causal_diag, int* status, void* stream) {
-  if (!dq) return RFA_ERR_INVALID_ARG;
+  if (!dq || (reinterpret_cast<uintptr_t>(dq) & 15u)) return RFA_ERR_INVALID_ARG;
+  // every argument is checked before anything is enqueued on the stream
+  {
+    const int rc0 = rfa::bwd_check_args(q, k, v, dout, lse2, delta, dkdv_prev, dkdv_out, B, Sq, Skv, Hq, Hkv, D, dtype,
+                                        softmax_scale, accumulate_prev, causal_diag, /*q_begin=*/0, /*kv_len=*/Skv,
+                                        status);
+    if (rc0 != RFA_OK) return rc0;
+  }
   const size_t elems = rfa_dq_acc_elems(B, Sq, Hq, D);
   if (elems == 0) return RFA_ERR_UNSUPPORTED;
   if (elems * sizeof(float) > kScratchBytes) return RFA_ERR_TOO_LARGE;  // shape needs more than the fixed array

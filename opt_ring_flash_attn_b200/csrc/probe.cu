@@ -1,5 +1,5 @@
 // Diagnostic kernel: one 128x128x128 product through each operand path used by
-// the hop kernels (see rfa_debug_mma_probe in the public header).  It exists so
+// the hop kernels (see rfa_debug_mma_probe in rfa_b200_debug.h).  It exists so
 // that a wrong descriptor field or swizzle shows up as a wrong 128x128 matrix in
 // a unit test instead of as a wrong attention result.
 #include "common.h"
@@ -147,13 +147,15 @@ extern "C" int rfa_debug_mma_probe(int mode, const void* a, const void* b, float
   if ((rc = make_tmap_bshd(&ta, a, RFA_DTYPE_BF16, 1, 128, 1, 128, 128)) != RFA_OK) return rc;
   if ((rc = make_tmap_bshd(&tb, b, RFA_DTYPE_BF16, 1, 128, 1, 128, 128)) != RFA_OK) return rc;
   const int smem = 65536 + 1024 + 60 * 1024;  // above half an SM: one CTA per SM
-  static bool attr_done = false;
-  if (!attr_done) {
+  static bool attr_done[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return RFA_ERR_CUDA; }
+  if (!attr_done[dev]) {
     if (cudaFuncSetAttribute(mma_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
       cudaGetLastError();
       return RFA_ERR_CUDA;
     }
-    attr_done = true;
+    attr_done[dev] = true;
   }
   mma_probe_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(ta, tb, static_cast<const __nv_bfloat16*>(a),
                                                                       c, mode, status);

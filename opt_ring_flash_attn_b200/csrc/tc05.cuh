@@ -470,6 +470,15 @@ __device__ __forceinline__ void red_add_v4_f32(float* gptr, float a, float b, fl
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gptr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
+// Cross-CTA counters in global memory: acquire load and release add at GPU scope.
+__device__ __forceinline__ int ld_acquire_gpu(const int* gptr) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(gptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int* gptr, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(gptr), "r"(v) : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "

@@ -18,6 +18,7 @@ dQ, dK and dV of a hop come from one fused kernel.
 """
 from __future__ import annotations
 
+import atexit
 import os
 from typing import Optional, Tuple
 
@@ -28,20 +29,54 @@ from . import _native, workspace
 from .transport import make_transport
 
 
+# (ring key, device, ring name) -> transport.  The key is the process-group object itself (not its id(), which
+# Python may hand to another object once a group is gone); entries live until shutdown().
 _transports = {}
 
 
+def _is_ring_handle(group) -> bool:
+    """A ring handle stands in for a process group: any object with ``world_size``, ``ring_rank``,
+    ``transport(name)`` and ``workspace_key``.  It lets one process drive several ranks (each with its own
+    scratch and its own transports), which is how the schedules are exercised on a single device."""
+    return hasattr(group, "ring_rank")
+
+
+def _ws_owner(group):
+    return group.workspace_key if _is_ring_handle(group) else None
+
+
 def _transport(group, device: torch.device, tag: str):
-    """One transport (and side stream) per (group, device, ring) for the life of the process."""
-    key = (id(group) if group is not None else None, str(device), tag)
+    """One transport (and side stream) per (group, device, ring) until :func:`shutdown`."""
+    if _is_ring_handle(group):
+        return group.transport(tag)
+    ring = group if group is not None else dist.group.WORLD
+    key = (ring, str(device), tag)
     t = _transports.get(key)
     if t is None or t.world_size != dist.get_world_size(group):
+        if t is not None:
+            t.close()
         t = make_transport(group, device)
         _transports[key] = t
     return t
 
 
+def shutdown() -> None:
+    """Destroy every cached transport (NCCL communicators, streams, events).  Call it before destroying the
+    process group the transports were created on; it also runs at interpreter exit."""
+    for t in list(_transports.values()):
+        try:
+            t.close()
+        except Exception:
+            pass
+    _transports.clear()
+
+
+atexit.register(shutdown)
+
+
 def _world(group) -> Tuple[int, int]:
+    if _is_ring_handle(group):
+        return group.world_size, group.ring_rank
     if dist.is_available() and dist.is_initialized():
         return dist.get_world_size(group), dist.get_rank(group)
     return 1, 0
@@ -53,12 +88,14 @@ def ring_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softm
     kn = kernels if kernels is not None else _native
     W, rank = _world(group)
     B, S, Hq, D = q.shape
-    ws = workspace.forward_workspace(q, k, W)
+    ws = workspace.forward_workspace(q, k, W, owner=_ws_owner(group))
+    workspace.raise_if_failed(ws, "ring_flash_attn forward")
     out = torch.empty_like(q)
     lse = torch.empty(B, Hq, _native.padded_seq(S), dtype=torch.float32, device=q.device)
 
     if W == 1:
         kn.fwd_hop(q, k, v, None, None, None, out, lse, softmax_scale, True, True, causal, ws.status)
+        workspace.publish_status(ws, "ring_flash_attn forward")
         return out, lse
 
     comm = _transport(group, q.device, "fwd_kv")
@@ -76,6 +113,7 @@ def ring_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softm
             comm.wait()
             cur = ws.kv_recv[step & 1]
             k_cur, v_cur = cur[0], cur[1]
+    workspace.publish_status(ws, "ring_flash_attn forward")
     return out, lse
 
 
@@ -109,12 +147,16 @@ def _finish_dkdv(kn, final, dk, dv) -> None:
 
 
 def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
-                  lse: torch.Tensor, softmax_scale: float, causal: bool, kernels=None):
-    """Returns ``(dq, dk, dv)`` in the input dtypes."""
+                  lse: torch.Tensor, softmax_scale: float, causal: bool, kernels=None, deterministic: bool = False):
+    """Returns ``(dq, dk, dv)`` in the input dtypes.  ``deterministic`` adds the dQ contributions of the K/V tiles
+    in a fixed order (bit-reproducible gradients, like the reference's tile-exclusive dQ update,
+    optimized_ring_flash_attn.py:730-735) at some cost in speed."""
     kn = kernels if kernels is not None else _native
     W, rank = _world(group)
-    ws = workspace.backward_workspace(q, k, W, backward_comm_dtype(q.dtype))
+    ws = workspace.backward_workspace(q, k, W, backward_comm_dtype(q.dtype), owner=_ws_owner(group))
+    workspace.raise_if_failed(ws, "ring_flash_attn backward")
     wire16 = ws.dkdv[0].dtype != torch.float32
+    order = {"dq_order": ws.dq_order} if deterministic else {}
     dout = dout.contiguous()
     kn.bwd_prepare(out, dout, lse, ws.delta, ws.lse2, ws.dq_acc, ws.status)
 
@@ -124,10 +166,12 @@ def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
 
     if W == 1:
         buf = ws.dkdv[0]
-        kn.bwd_hop(q, k, v, dout, ws.lse2, ws.delta, ws.dq_acc, None, buf, softmax_scale, False, causal, ws.status)
+        kn.bwd_hop(q, k, v, dout, ws.lse2, ws.delta, ws.dq_acc, None, buf, softmax_scale, False, causal, ws.status,
+                   **order)
         kn.dq_finalize(ws.dq_acc, dq)
         kn.cast_from_f32(buf[0], dk)
         kn.cast_from_f32(buf[1], dv)
+        workspace.publish_status(ws, "ring_flash_attn backward")
         return dq, dk, dv
 
     kv_comm = _transport(group, q.device, "bwd_kv")
@@ -146,7 +190,7 @@ def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
             # transport), later it writes this rank's block and the partial sums are folded in once they have arrived.
             direct = step == 0 and not wire16
             kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, buf if direct else ws.block_dkdv,
-                       softmax_scale, False, causal and step == 0, ws.status)
+                       softmax_scale, False, causal and step == 0, ws.status, **order)
             if step == 0 and wire16:
                 _fold_block(kn, buf, ws.block_dkdv, first=True)
         if step > 0:
@@ -162,6 +206,7 @@ def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
     final = ws.dkdv[(W - 1) & 1]
     kn.dq_finalize(ws.dq_acc, dq)
     _finish_dkdv(kn, final, dk, dv)
+    workspace.publish_status(ws, "ring_flash_attn backward")
     return dq, dk, dv
 
 
@@ -184,11 +229,13 @@ def zigzag_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sof
     kn = kernels if kernels is not None else _native
     W, rank = _world(group)
     B, S, Hq, D = q.shape
-    ws = workspace.forward_workspace(q, k, W)
+    ws = workspace.forward_workspace(q, k, W, owner=_ws_owner(group))
+    workspace.raise_if_failed(ws, "ring_flash_attn forward")
     out = torch.empty_like(q)
     lse = torch.empty(B, Hq, _native.padded_seq(S), dtype=torch.float32, device=q.device)
     if W == 1:
         kn.fwd_hop(q, k, v, None, None, None, out, lse, softmax_scale, True, True, True, ws.status)
+        workspace.publish_status(ws, "ring_flash_attn forward")
         return out, lse
     half = _zigzag_half(S)
     comm = _transport(group, q.device, "fwd_kv")
@@ -214,20 +261,24 @@ def zigzag_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sof
             comm.wait()
             cur = ws.kv_recv[step & 1]
             k_cur, v_cur = cur[0], cur[1]
+    workspace.publish_status(ws, "ring_flash_attn forward")
     return out, lse
 
 
 def zigzag_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
-                    lse: torch.Tensor, softmax_scale: float, kernels=None):
+                    lse: torch.Tensor, softmax_scale: float, kernels=None, deterministic: bool = False):
     """Backward of :func:`zigzag_forward`; same window rule per step (optimized_ring_flash_attn.py:1198-1275),
     same two rings and slot algebra as :func:`ring_backward`."""
     kn = kernels if kernels is not None else _native
     W, rank = _world(group)
     if W == 1:
-        return ring_backward(group, dout, q, k, v, out, lse, softmax_scale, True, kernels=kernels)
+        return ring_backward(group, dout, q, k, v, out, lse, softmax_scale, True, kernels=kernels,
+                             deterministic=deterministic)
     S = q.shape[1]
     half = _zigzag_half(S)
-    ws = workspace.backward_workspace(q, k, W, backward_comm_dtype(q.dtype))
+    ws = workspace.backward_workspace(q, k, W, backward_comm_dtype(q.dtype), owner=_ws_owner(group))
+    workspace.raise_if_failed(ws, "ring_flash_attn backward")
+    order = {"dq_order": ws.dq_order} if deterministic else {}
     wire16 = ws.dkdv[0].dtype != torch.float32
     dout = dout.contiguous()
     kn.bwd_prepare(out, dout, lse, ws.delta, ws.lse2, ws.dq_acc, ws.status)
@@ -246,15 +297,15 @@ def zigzag_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
         buf = ws.dkdv[prev_slot]
         if step == 0:
             kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, ws.block_dkdv if wire16 else buf,
-                       softmax_scale, False, True, ws.status, q_begin=0, kv_len=S)
+                       softmax_scale, False, True, ws.status, q_begin=0, kv_len=S, **order)
             if wire16:
                 _fold_block(kn, buf, ws.block_dkdv, first=True)
         elif step <= rank:
             kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, ws.block_dkdv, softmax_scale, False,
-                       False, ws.status, q_begin=0, kv_len=half)
+                       False, ws.status, q_begin=0, kv_len=half, **order)
         else:
             kn.bwd_hop(q, k_cur, v_cur, dout, ws.lse2, ws.delta, ws.dq_acc, None, ws.block_dkdv, softmax_scale, False,
-                       False, ws.status, q_begin=half, kv_len=S)
+                       False, ws.status, q_begin=half, kv_len=S, **order)
         if step > 0:
             dkv_comm.wait()
             _fold_block(kn, buf, ws.block_dkdv, first=False)
@@ -267,4 +318,5 @@ def zigzag_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
     final = ws.dkdv[(W - 1) & 1]
     kn.dq_finalize(ws.dq_acc, dq)
     _finish_dkdv(kn, final, dk, dv)
+    workspace.publish_status(ws, "ring_flash_attn backward")
     return dq, dk, dv

@@ -83,6 +83,10 @@ class RingTransport:
         while self._pending:
             self.wait()
 
+    def close(self) -> None:
+        """Nothing of its own to release: the process group owns the communicator."""
+        self._pending.clear()
+
 
 class NativeRingTransport:
     """Same protocol on a private NCCL communicator inside ``librfa_b200.so`` (``rfa_ring_post`` / ``rfa_ring_wait``).
@@ -122,16 +126,19 @@ class NativeRingTransport:
     def wait(self) -> None:
         if not self._pending:
             raise RuntimeError("ring transport: wait() without a posted transfer")
-        self._native.ring_wait(self._handle, self._pending.popleft())
+        self._native.ring_wait(self._handle, self._pending.popleft(), device=self.device)
 
     def drain(self) -> None:
         while self._pending:
             self.wait()
 
     def close(self) -> None:
+        """Destroy the communicator, the transport stream and its events (collective-free, local)."""
         if self._handle is not None:
-            self._native.comm_destroy(self._handle)
-            self._handle = None
+            handle, self._handle = self._handle, None
+            self._pending.clear()
+            with torch.cuda.device(self.device):
+                self._native.comm_destroy(handle)
 
 
 def make_transport(group: Optional[dist.ProcessGroup], device: torch.device):

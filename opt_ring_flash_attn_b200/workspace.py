@@ -8,12 +8,20 @@ what autograd saved for the first one.
 
 All scratch is consumed inside the call that fills it, in stream order, so one
 slot per (shape, dtype, device, world size) is enough as long as calls on one
-device are issued on one stream.
+device are issued on one stream.  A ring handle (several ranks driven by one
+process) gets a slot of its own through ``owner``.
+
+Each workspace also carries the device status word of its kernels and a pinned host copy of it.  A kernel
+whose bounded pipeline wait runs out sets the word and every later kernel of that workspace returns at once, so
+the word has to reach the host: :func:`publish_status` copies it out asynchronously at the end of a pass and
+:func:`raise_if_failed` looks at the last copy at the start of the next one (no synchronisation; with
+``RFA_B200_SYNC_STATUS=1`` every pass ends with a synchronising check instead).  :func:`check_all` does it on demand.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import Dict, List, Optional, Tuple
+import os
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Tuple
 
 import torch
 
@@ -32,6 +40,8 @@ class ForwardWorkspace:
     kv_send: Optional[torch.Tensor]   # dtype [2, B, S, Hkv, D]
     kv_recv: List[torch.Tensor]       # 2 x dtype [2, B, S, Hkv, D]
     status: torch.Tensor              # int32 [1]
+    status_host: Optional[torch.Tensor] = None   # pinned int32 [1]: last published copy of ``status``
+    status_event: Any = None                     # recorded after the copy into status_host
 
 
 @dataclass
@@ -44,50 +54,107 @@ class BackwardWorkspace:
     kv_send: Optional[torch.Tensor]
     kv_recv: List[torch.Tensor]
     status: torch.Tensor
+    dq_order: Optional[torch.Tensor] = None      # int32 counters of the ordered (deterministic) dQ reductions
+    status_host: Optional[torch.Tensor] = None
+    status_event: Any = None
 
 
-_fwd_cache: Dict[Tuple, ForwardWorkspace] = {}
-_bwd_cache: Dict[Tuple, BackwardWorkspace] = {}
+# owner -> (key, workspace): one slot per owner (None = the process's own rank; a ring handle brings its own key)
+_fwd_cache: Dict[Any, Tuple[Tuple, ForwardWorkspace]] = {}
+_bwd_cache: Dict[Any, Tuple[Tuple, BackwardWorkspace]] = {}
 
 
 def _key(q: torch.Tensor, k: torch.Tensor, world_size: int, extra=None) -> Tuple:
     return (tuple(q.shape), tuple(k.shape), q.dtype, str(q.device), world_size, extra)
 
 
-def forward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int) -> ForwardWorkspace:
+def _new_status(dev: torch.device):
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    host = torch.zeros(1, dtype=torch.int32, pin_memory=True) if dev.type == "cuda" else None
+    return status, host
+
+
+def all_workspaces() -> List:
+    return [ws for _, ws in list(_fwd_cache.values()) + list(_bwd_cache.values())]
+
+
+def _fail(ws, code: int, what: str):
+    ws.status.zero_()  # reported once; the workspace is usable again
+    ws.status_event = None
+    raise RuntimeError(f"{what}: device status {code}: {_native.STATUS_NAMES.get(code, 'unknown')}; the results of "
+                       "the pass that hit it are invalid")
+
+
+def _capturing(ws) -> bool:
+    return ws.status.is_cuda and torch.cuda.is_current_stream_capturing()
+
+
+def raise_if_failed(ws, what: str) -> None:
+    """Start of a pass: if the copy published by the previous pass on this workspace has landed and is non-zero,
+    clear the device word and raise.  Never blocks."""
+    ev = ws.status_event
+    if ev is None or _capturing(ws) or not ev.query():
+        return
+    ws.status_event = None
+    code = int(ws.status_host[0])
+    if code != 0:
+        _fail(ws, code, what)
+
+
+def publish_status(ws, what: str) -> None:
+    """End of a pass: enqueue the copy of the status word to pinned host memory (4 bytes) and an event behind it."""
+    if ws.status_host is None or _capturing(ws) or os.environ.get("RFA_B200_STATUS_CHECK", "1") == "0":
+        return
+    ws.status_host.copy_(ws.status, non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(ws.status.device))
+    ws.status_event = ev
+    if os.environ.get("RFA_B200_SYNC_STATUS", "0") == "1":
+        ev.synchronize()
+        raise_if_failed(ws, what)
+
+
+def check_all(what: str = "ring_flash_attn") -> None:
+    """Synchronising check of every cached workspace's status word; raises ``RuntimeError`` on the first failure."""
+    for ws in all_workspaces():
+        code = int(ws.status.item())
+        if code != 0:
+            _fail(ws, code, what)
+
+
+def forward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int, owner=None) -> ForwardWorkspace:
     key = _key(q, k, world_size)
-    ws = _fwd_cache.get(key)
-    if ws is not None:
-        return ws
+    hit = _fwd_cache.get(owner)
+    if hit is not None and hit[0] == key:
+        return hit[1]
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
     dev = q.device
     spad = _native.padded_seq(S)
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    status, status_host = _new_status(dev)
     if world_size == 1:
-        ws = ForwardWorkspace(None, None, None, None, [], status)
+        ws = ForwardWorkspace(None, None, None, None, [], status, status_host)
     else:
         acc = torch.empty(B * Hq * spad * _padded_head_dim(D), dtype=torch.float32, device=dev)
         m = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
         l = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
         kv_send = torch.empty(2, B, S, Hkv, D, dtype=q.dtype, device=dev)
         kv_recv = [torch.empty_like(kv_send) for _ in range(2)]
-        ws = ForwardWorkspace(acc, m, l, kv_send, kv_recv, status)
-    _fwd_cache.clear()  # single slot, like the reference
-    _fwd_cache[key] = ws
+        ws = ForwardWorkspace(acc, m, l, kv_send, kv_recv, status, status_host)
+    _fwd_cache[owner] = (key, ws)  # single slot per owner, like the reference
     return ws
 
 
 def backward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int,
-                       comm_dtype: torch.dtype = torch.float32) -> BackwardWorkspace:
+                       comm_dtype: torch.dtype = torch.float32, owner=None) -> BackwardWorkspace:
     """``comm_dtype`` is the dtype of the travelling dK/dV buffers (fp32, or the input dtype for 16-bit transport,
     optimized_ring_flash_attn.py:205-208, 271-272); this hop's own block is always fp32."""
     if world_size == 1:
         comm_dtype = torch.float32
     key = _key(q, k, world_size, comm_dtype)
-    ws = _bwd_cache.get(key)
-    if ws is not None:
-        return ws
+    hit = _bwd_cache.get(owner)
+    if hit is not None and hit[0] == key:
+        return hit[1]
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
     dev = q.device
@@ -103,10 +170,11 @@ def backward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int,
         kv_send = torch.empty(2, B, S, Hkv, D, dtype=q.dtype, device=dev)
         kv_recv = [torch.empty_like(kv_send) for _ in range(2)]
         block_dkdv = torch.empty(2, B, S, Hkv, D, dtype=torch.float32, device=dev)
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-    ws = BackwardWorkspace(delta, lse2, dq_acc, dkdv, block_dkdv, kv_send, kv_recv, status)
-    _bwd_cache.clear()
-    _bwd_cache[key] = ws
+    status, status_host = _new_status(dev)
+    # counters of the ordered dQ reductions: 8 per (batch, head, query tile of 64 rows) covers every head dim
+    dq_order = torch.zeros(B * Hq * ((S + 63) // 64) * 2 * 8, dtype=torch.int32, device=dev)
+    ws = BackwardWorkspace(delta, lse2, dq_acc, dkdv, block_dkdv, kv_send, kv_recv, status, dq_order, status_host)
+    _bwd_cache[owner] = (key, ws)
     return ws
 
 

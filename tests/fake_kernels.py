@@ -82,7 +82,7 @@ def bwd_prepare(out, dout, lse, delta, lse2, dq_acc, status, stream=None):
 
 
 def bwd_hop(q, k, v, dout, lse2, delta, dq_acc, dkdv_prev, dkdv_out, scale, accumulate_prev, causal_diag, status,
-            stream=None, q_begin=0, kv_len=None):
+            stream=None, q_begin=0, kv_len=None, dq_order=None):
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
     kv_len = k.shape[1] if kv_len is None else kv_len

@@ -45,10 +45,10 @@ def _worker(rank, world, port, cfg, errs):
             out, lse = ring_flash_attn_with_lse(ql, kl, vl, causal=causal, group=dist.group.WORLD, zigzag=zigzag)
             out.backward(dos[rank])
         torch.cuda.synchronize()
-        for ws in list(workspace._fwd_cache.values()) + list(workspace._bwd_cache.values()):
+        for ws in workspace.all_workspaces():
             _native.check_status(ws.status, "ring")
         if wire16:
-            assert next(iter(workspace._bwd_cache.values())).dkdv[0].dtype == dtype
+            assert next(iter(workspace._bwd_cache.values()))[1].dkdv[0].dtype == dtype
         if zigzag:
             ref = zigzag_oracle(q, k, v, dout, world, head_chunk=4)
         else:

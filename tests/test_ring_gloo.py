@@ -58,7 +58,7 @@ def _worker(rank, world, port, causal, Hq, Hkv, use_subgroup, errs, wire16=False
 
         if wire16 and ring_world > 1:
             from opt_ring_flash_attn_b200 import workspace
-            ws = next(iter(workspace._bwd_cache.values()))
+            ws = next(iter(workspace._bwd_cache.values()))[1]
             assert ws.dkdv[0].dtype == torch.bfloat16 and ws.block_dkdv.dtype == torch.float32
         assert torch.equal(out, out2)
         assert (out.float() - ref["out"][r]).abs().max().item() <= 1e-2
