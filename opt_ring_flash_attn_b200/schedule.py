@@ -69,9 +69,35 @@ def shutdown() -> None:
         except Exception:
             pass
     _transports.clear()
+    _shapes_agreed.clear()
 
 
 atexit.register(shutdown)
+
+
+_shapes_agreed = set()
+
+
+def _agree_on_shapes(group, q: torch.Tensor, k: torch.Tensor, W: int) -> None:
+    """The ring needs the same local shapes and dtype on every rank (the reference's contract: equal contiguous
+    shards).  A mismatch would otherwise show up as a transfer of the wrong size -- a hang or silent garbage -- so
+    the first call with a new shape on a process group compares them across ranks (one small object all-gather,
+    never repeated for that shape) and raises ``ValueError`` on every rank before any buffer moves.
+    ``RFA_B200_CHECK_SHAPES=0`` skips it."""
+    if W == 1 or _is_ring_handle(group) or os.environ.get("RFA_B200_CHECK_SHAPES", "1") == "0":
+        return
+    if q.is_cuda and torch.cuda.is_current_stream_capturing():
+        return
+    ring = group if group is not None else dist.group.WORLD
+    mine = (tuple(q.shape), tuple(k.shape), str(q.dtype))
+    key = (ring, mine)
+    if key in _shapes_agreed:
+        return
+    everyone = [None] * W
+    dist.all_gather_object(everyone, mine, group=group)
+    if any(other != mine for other in everyone):
+        raise ValueError(f"ring_flash_attn: ranks disagree on the local shapes/dtype (q, k, dtype) per rank: {everyone}")
+    _shapes_agreed.add(key)
 
 
 def _world(group) -> Tuple[int, int]:
@@ -88,6 +114,7 @@ def ring_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softm
     kn = kernels if kernels is not None else _native
     W, rank = _world(group)
     B, S, Hq, D = q.shape
+    _agree_on_shapes(group, q, k, W)
     ws = workspace.forward_workspace(q, k, W, owner=_ws_owner(group))
     workspace.raise_if_failed(ws, "ring_flash_attn forward")
     out = torch.empty_like(q)
@@ -229,6 +256,7 @@ def zigzag_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sof
     kn = kernels if kernels is not None else _native
     W, rank = _world(group)
     B, S, Hq, D = q.shape
+    _agree_on_shapes(group, q, k, W)
     ws = workspace.forward_workspace(q, k, W, owner=_ws_owner(group))
     workspace.raise_if_failed(ws, "ring_flash_attn forward")
     out = torch.empty_like(q)

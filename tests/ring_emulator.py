@@ -1,9 +1,8 @@
-"""Runs the W-rank ring schedule on ONE device by visiting the ranks one after another.
+"""A hand-written walk over the W ranks of the contiguous-shard ring on ONE device, rank after rank.
 
-Each emulated rank issues exactly the hop-kernel calls that ``schedule.ring_forward`` /
-``schedule.ring_backward`` issue for it (same first/last/causal flags, same buffer roles); the
-transport is replaced by handing the packed buffers from one emulated rank to the next.  No two
-kernels wait on one another, so this is safe on a single GPU.  Test helper only.
+The product schedules themselves are driven by tests/inproc_ring.py; this walk exists for the one code path they
+do not take: the backward kernel's epilogue that adds the travelling partial dK/dV itself (``accumulate_prev``).
+No two kernels wait on one another, so this is safe on a single GPU.  Test helper only.
 """
 from __future__ import annotations
 
@@ -77,67 +76,3 @@ def emulate_backward(douts, qs, ks, vs, outs, lses_padded, scale: float, causal:
         kn.cast_from_f32(travelling[r][1], dv)
         dqs.append(dq); dks.append(dk); dvs.append(dv)
     return dqs, dks, dvs, status
-
-
-def emulate_zigzag(qs, ks, vs, douts, scale: float, kn=_native):
-    """Zigzag schedule (schedule.zigzag_forward / zigzag_backward) rank by rank on one device.
-    qs/ks/vs/douts are the zigzag-arranged shards.  Returns (outs, lses, dqs, dks, dvs, status)."""
-    W = len(qs)
-    B, S, Hq, D = qs[0].shape
-    Hkv = ks[0].shape[2]
-    dev = qs[0].device
-    half = S // 2
-    spad = _native.padded_seq(S)
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-    outs, lses_pad = [], []
-    for r in range(W):
-        out = torch.empty_like(qs[r])
-        lse = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
-        acc = torch.empty(B * Hq * spad * _padded_head_dim(D), dtype=torch.float32, device=dev)
-        m = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
-        l = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
-        for step in range(W):
-            kb = (r - step) % W
-            last_hi, last_lo = step == W - 1, step == r
-            if step == 0:
-                kn.fwd_hop(qs[r], ks[kb], vs[kb], acc, m, l, out, lse, scale, True, last_hi, True, status,
-                           q_begin=0, kv_len=S, q_split=half, last_lo=last_lo)
-            elif step <= r:
-                kn.fwd_hop(qs[r], ks[kb], vs[kb], acc, m, l, out, lse, scale, False, last_hi, False, status,
-                           q_begin=0, kv_len=half, q_split=half, last_lo=last_lo)
-            else:
-                kn.fwd_hop(qs[r], ks[kb], vs[kb], acc, m, l, out, lse, scale, False, last_hi, False, status,
-                           q_begin=half, kv_len=S, q_split=half, last_lo=False)
-        outs.append(out)
-        lses_pad.append(lse)
-    delta = [torch.empty(B, Hq, spad, dtype=torch.float32, device=dev) for _ in range(W)]
-    lse2 = [torch.empty(B, Hq, spad, dtype=torch.float32, device=dev) for _ in range(W)]
-    dq_acc = [torch.empty(B * Hq * spad * _padded_head_dim(D), dtype=torch.float32, device=dev) for _ in range(W)]
-    for r in range(W):
-        kn.bwd_prepare(outs[r], douts[r], lses_pad[r], delta[r], lse2[r], dq_acc[r], status)
-    travelling = {}
-    block = torch.empty(2, B, S, Hkv, D, dtype=torch.float32, device=dev)
-    for step in range(W):
-        for r in range(W):
-            kb = (r - step) % W
-            if step == 0:
-                travelling[kb] = torch.full((2, B, S, Hkv, D), float("nan"), dtype=torch.float32, device=dev)
-                kn.bwd_hop(qs[r], ks[kb], vs[kb], douts[r], lse2[r], delta[r], dq_acc[r], None, travelling[kb], scale,
-                           False, True, status, q_begin=0, kv_len=S)
-                continue
-            block.fill_(float("nan"))
-            if step <= r:
-                kn.bwd_hop(qs[r], ks[kb], vs[kb], douts[r], lse2[r], delta[r], dq_acc[r], None, block, scale, False,
-                           False, status, q_begin=0, kv_len=half)
-            else:
-                kn.bwd_hop(qs[r], ks[kb], vs[kb], douts[r], lse2[r], delta[r], dq_acc[r], None, block, scale, False,
-                           False, status, q_begin=half, kv_len=S)
-            kn.dkdv_accumulate(travelling[kb], block, travelling[kb])
-    dqs, dks, dvs = [], [], []
-    for r in range(W):
-        dq = torch.empty_like(qs[r]); dk = torch.empty_like(ks[r]); dv = torch.empty_like(vs[r])
-        kn.dq_finalize(dq_acc[r], dq)
-        kn.cast_from_f32(travelling[r][0], dk)
-        kn.cast_from_f32(travelling[r][1], dv)
-        dqs.append(dq); dks.append(dk); dvs.append(dv)
-    return outs, [x[:, :, :S] for x in lses_pad], dqs, dks, dvs, status

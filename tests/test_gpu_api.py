@@ -138,3 +138,55 @@ def test_cuda_graph_capture_single_gpu():
     assert _rel_l2(sq.grad, ref["dq"][0]) <= 2e-2
     assert _rel_l2(sk.grad, ref["dk"][0]) <= 2e-2
     assert _rel_l2(sv.grad, ref["dv"][0]) <= 2e-2
+
+
+def test_device_status_word_surfaces_as_an_error(monkeypatch):
+    """A kernel whose bounded wait runs out sets the workspace's status word and every later kernel returns at
+    once.  The failure is made on the host here (the word is written from Python, nothing faults or times out on
+    the GPU): the pass that ran with the word set publishes it, and the next call on that scratch raises and
+    clears it; with RFA_B200_SYNC_STATUS=1 the failing call itself raises."""
+    import opt_ring_flash_attn_b200 as rfa
+    from opt_ring_flash_attn_b200 import workspace
+
+    dev = torch.device("cuda:0")
+    q, k, v, _ = (x.to(dev) for x in make_inputs(36, 1, 256, 2, 2, 64, dtype=torch.bfloat16))
+    monkeypatch.setenv("RFA_B200_SYNC_STATUS", "0")
+    good = rfa.ring_flash_attn(q, k, v, causal=True)
+    torch.cuda.synchronize()
+    ws = workspace.forward_workspace(q, k, 1)
+    ws.status.fill_(1)                       # "a pipeline wait ran out" injected from the host
+    rfa.ring_flash_attn(q, k, v, causal=True)  # kernels return at once; the result of this call is invalid
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="device status 1"):
+        rfa.ring_flash_attn(q, k, v, causal=True)
+    assert int(ws.status.item()) == 0        # cleared once reported: the operator works again
+    again = rfa.ring_flash_attn(q, k, v, causal=True)
+    torch.cuda.synchronize()
+    assert torch.equal(again, good)
+    # synchronous mode: the failing call raises itself
+    monkeypatch.setenv("RFA_B200_SYNC_STATUS", "1")
+    ws.status.fill_(1)
+    with pytest.raises(RuntimeError, match="device status 1"):
+        rfa.ring_flash_attn(q, k, v, causal=True)
+    monkeypatch.setenv("RFA_B200_SYNC_STATUS", "0")
+    ws.status.fill_(1)
+    with pytest.raises(RuntimeError, match="device status 1"):
+        rfa.check()
+    assert torch.equal(rfa.ring_flash_attn(q, k, v, causal=True), good)
+
+
+def test_deterministic_wrapper_flag_gives_identical_gradients():
+    """`deterministic=True` of the baseline-style wrappers: two backward passes give the same bits."""
+    import opt_ring_flash_attn_b200 as rfa
+
+    dev = torch.device("cuda:0")
+    q, k, v, dout = (x.to(dev) for x in make_inputs(37, 1, 1024, 8, 2, 128, dtype=torch.bfloat16))
+    grads = []
+    for _ in range(2):
+        a, b, c = (x.clone().requires_grad_(True) for x in (q, k, v))
+        rfa.ring_flash_attn_func(a, b, c, causal=True, deterministic=True).backward(dout)
+        grads.append((a.grad, b.grad, c.grad))
+    for x, y in zip(*grads):
+        assert torch.equal(x, y)
+    ref = ring_attn_oracle([q], [k], [v], [dout], causal=True)
+    assert _rel_l2(grads[0][0], ref["dq"][0]) <= 2e-2

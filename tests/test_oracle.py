@@ -83,3 +83,25 @@ def test_merge_identity():
     w2 = torch.exp(l2 - lse).transpose(1, 2).unsqueeze(-1)
     assert torch.allclose(o1 * w1 + o2 * w2, o_all, atol=1e-6)
     assert torch.allclose(lse, lse_all, atol=1e-6)
+
+
+def test_slice_wise_restatement_matches_the_pinned_oracle():
+    """oracle/chunked_attn.py (row / key slices of a causal single-shard problem, used where the full score matrix
+    cannot exist) against ring_attn_oracle on a shape small enough for both: GQA, odd block sizes, custom scale."""
+    from oracle import chunked_attn as ca
+
+    B, S, Hq, Hkv, D, scale = 2, 320, 4, 2, 32, 0.2
+    q, k, v, dout = make_inputs(17, B, S, Hq, Hkv, D)
+    ref = ring_attn_oracle([q], [k], [v], [dout], causal=True, softmax_scale=scale)
+    lse, delta = ca.full_stats(q, k, v, dout, scale, row_block=96)
+    assert (lse - ref["lse"][0]).abs().max().item() <= 2e-5
+    for r0, r1 in ((0, 64), (100, 228), (256, 320)):
+        out, l = ca.forward_rows(q, k, v, scale, r0, r1)
+        assert (out - ref["out"][0][:, r0:r1]).abs().max().item() <= 2e-5
+        assert (l - ref["lse"][0][:, :, r0:r1]).abs().max().item() <= 2e-5
+        dq = ca.dq_rows(q, k, v, dout, lse, delta, scale, r0, r1)
+        assert (dq - ref["dq"][0][:, r0:r1]).abs().max().item() <= 2e-5
+    for k0, k1 in ((0, 32), (130, 200), (288, 320)):
+        dk, dv = ca.dkdv_keys(q, k, v, dout, lse, delta, scale, k0, k1, row_block=100)
+        assert (dk - ref["dk"][0][:, k0:k1]).abs().max().item() <= 5e-5
+        assert (dv - ref["dv"][0][:, k0:k1]).abs().max().item() <= 5e-5

@@ -3,15 +3,15 @@
 ``rfa_bwd_hop_noalloc`` is for hosts that may not call cudaMalloc (a fully pre-assigned memory pool, a
 plugin boundary that only hands tensors in and out).  It keeps its fp32 dQ accumulator in a fixed
 array inside the library, so this test checks what that changes: the result must equal the regular
-entry point's (``rfa_bwd_hop`` + ``rfa_bwd_dq_finalize`` with a caller-allocated accumulator), and a
-second call must not see what the first one left in the shared array.  Shapes beyond the array are
+entry point's (``rfa_bwd_hop`` + ``rfa_bwd_dq_finalize`` with a caller-allocated accumulator) and the
+oracle's, and a second call must not see what the first one left in the shared array.  Shapes beyond the array are
 refused.  The file name sorts last so that a run stopping at the first failure has already covered
 everything else.
 """
 import pytest
 import torch
 
-from oracle.ring_attn_oracle import make_inputs
+from oracle.ring_attn_oracle import make_inputs, ring_attn_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -66,6 +66,11 @@ def test_noalloc_matches_regular_entry_point_twice():
         assert torch.isfinite(dq.float()).all() and torch.isfinite(dkdv).all()
         assert torch.equal(dkdv, dkdv_ref)                 # dK/dV do not touch the scratch: same bits
         assert _rel_l2(dq, dq_ref) <= GRAD_REL_L2          # dQ: fp32 reductions land in a different order
+        # and directly against the oracle (one rank: this hop is the whole backward pass)
+        ref = ring_attn_oracle([q], [k], [v], [dout], causal=causal)
+        assert _rel_l2(dq, ref["dq"][0]) <= GRAD_REL_L2
+        assert _rel_l2(dkdv[0], ref["dk"][0]) <= GRAD_REL_L2
+        assert _rel_l2(dkdv[1], ref["dv"][0]) <= GRAD_REL_L2
 
 
 def test_noalloc_rejects_shapes_beyond_the_array():
