@@ -41,7 +41,7 @@ CASES = [
     ("gqa_w2_causal", 5, 1, 128, 4, 2, 16, 2, True, None, 1),
     ("scaled_w2_causal", 6, 1, 128, 2, 2, 16, 2, True, 0.3, 1),
     # (no world-size-1 case: the reference's backward sends dQ to itself, which gloo rejects)
-    # BASELINE config 1: B=1, S_total=2048 (8 x 256), H=8, D=64, causal, seed 0; every 37th row is stored
+    # the reference's CPU configuration: B=1, S_total=2048 (8 x 256), H=8, D=64, causal, seed 0; every 37th row is stored
     ("config1_w8_causal", 0, 1, 2048, 8, 8, 64, 8, True, None, 37),
 ]
 
@@ -78,7 +78,9 @@ def _worker(rank: int, world: int, ref_dir: str, case, port: int, outdir: str):
 
 
 def main():
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference-checkout")
+    ref_dir = sys.argv[1]
     if not os.path.exists(os.path.join(ref_dir, "ring_attn.py")):
         raise SystemExit(f"{ref_dir}/ring_attn.py not found")
     fixtures = {}
