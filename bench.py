@@ -107,8 +107,9 @@ class ClockSampler:
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, period_ms: int = 100):
         self.index = index
+        self.period_ms = period_ms
         self.proc = None
         self.lines = []
 
@@ -116,7 +117,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(self.index),
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", str(self.period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -335,17 +336,23 @@ def timeline_step(native, schedule, group, q, k, v, dout, scale, zigzag):
     W = torch.distributed.get_world_size(group) if torch.distributed.is_initialized() else 1
     waits, posts = [], []
     if W > 1:
+        from opt_ring_flash_attn_b200 import workspace
+
+        # the transports of the scratch that earlier (untimed) steps of the same shape created
+        cached = {}
+        for ws_ in workspace.all_workspaces():
+            cached.update(ws_.comms)
         for tag in tags:
-            t = schedule._transport(group, dev, tag)
+            t = cached[tag]
             transports[tag] = t
-            if hasattr(t, "_handle"):
-                native.ring_timing(t._handle, True)
+            can_time = hasattr(t, "set_timing")
+            if can_time:
+                t.set_timing(True)
             orig_post, orig_wait = t.post, t.wait
 
-            def post(send, recv, _t=t, _tag=tag, _orig=orig_post):
+            def post(send, recv, _t=t, _tag=tag, _orig=orig_post, _can=can_time):
                 _orig(send, recv)
-                posts.append((_tag, _t._pending[-1] if hasattr(_t, "_handle") else None,
-                              send.numel() * send.element_size()))
+                posts.append((_tag, _t.last_slot() if _can else None, send.numel() * send.element_size()))
 
             def wait(_t=t, _tag=tag, _orig=orig_wait):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -378,15 +385,15 @@ def timeline_step(native, schedule, group, q, k, v, dout, scale, zigzag):
         transfers = []
         for tag, slot, nbytes in posts:
             if slot is not None:
-                ms = native.ring_elapsed_ms(transports[tag]._handle, slot)
+                ms = transports[tag].elapsed_ms(slot)
                 transfers.append({"ring": tag, "bytes": nbytes, "ms": ms, "gb_s": nbytes / ms / 1e6 if ms > 0 else None})
         return rows, transfers
     finally:
         for tag, t in transports.items():
             t.__dict__.pop("post", None)
             t.__dict__.pop("wait", None)
-            if hasattr(t, "_handle"):
-                native.ring_timing(t._handle, False)
+            if hasattr(t, "set_timing"):
+                t.set_timing(False)
 
 
 def summarize_timeline(rows, transfers):
@@ -615,9 +622,8 @@ def main():
         torch.cuda.synchronize()
 
     # clocks are sampled from the warm-up on, so that short timed regions still get samples under load
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    sampler = ClockSampler(local_rank, period_ms=100 if world == 1 else 25)
+    sampler.start()
     for _ in range(warmup):
         step_device()
     barrier()
@@ -626,7 +632,13 @@ def main():
     launches = _native.launch_count() - launches0
     if args.graph:
         launches = launches_per_replay * args.steps  # the kernels run from the graph, not through the C ABI
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop()
+    if world > 1:  # the slowest rank is the one under sustained load: every rank's record goes into the line
+        per_rank = [None] * world
+        dist.all_gather_object(per_rank, {"sm_mhz": clocks.get("sm_mhz"), "sm_min_mhz": clocks.get("sm_min_mhz"),
+                                          "power_w_max": clocks.get("power_w_max"), "reasons": clocks.get("reasons")})
+        clocks["per_rank"] = per_rank
+        clocks["reasons"] = sorted({r for c in per_rank for r in (c.get("reasons") or [])})
 
     # ---- zigzag layout beside the headline (same process; the same shards read as the zigzag arrangement) ----
     zigzag_rec = None
@@ -646,10 +658,10 @@ def main():
         for _ in range(2):
             timeline_step(_native, schedule, group, q, k, v, dout, sc, args.zigzag)
         barrier()
-        hs = ClockSampler(local_rank)
+        hs = ClockSampler(local_rank, period_ms=20)
         hs.start()
         tables = []
-        for _ in range(3):
+        for _ in range(5):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             barrier()
             e0.record()

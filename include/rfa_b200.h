@@ -240,6 +240,36 @@ int rfa_comm_destroy(void* handle);
 int rfa_ring_post(void* handle, const void* send, void* recv, size_t bytes, void* compute_stream);
 int rfa_ring_wait(void* handle, int slot, void* compute_stream);
 
+/*
+ * Ring transport over peer memory (same role as DoubleBufRingComm, optimized_ring_flash_attn.py:163-188, and as the
+ * rfa_comm_* transport above): for ranks that are processes on one node whose GPUs can map each other's memory.
+ * A transfer is one copy-engine copy out of the previous rank's buffer, ordered by sequence flags the neighbours
+ * write into each other's memory and the transport's stream waits on with stream memory operations: no thread
+ * block is involved, so a transfer neither waits for an SM nor takes one from the hop kernel.
+ *
+ *  rfa_peer_create(rank, W, &handle)    local; the handle owns a stream, events and a small flag buffer
+ *  rfa_peer_alloc(handle, bytes, &ptr)  allocates ring buffer number i (cudaMalloc: the ring buffers must be
+ *                                       exportable, so the handle owns them); every rank allocates the same buffers
+ *                                       in the same order; at most 8
+ *  rfa_peer_export(handle, out, cap)    fills rfa_peer_export_bytes() bytes of host memory to hand to both neighbours
+ *  rfa_peer_connect(handle, prev, next) maps the previous rank's buffers and both neighbours' flags (after every
+ *                                       rank has exported; no more rfa_peer_alloc afterwards)
+ *  rfa_peer_post(handle, send, recv, bytes, compute_stream) / rfa_peer_wait(handle, slot, compute_stream)
+ *        as rfa_ring_post / rfa_ring_wait; send and recv must be buffers of this handle, and every rank must pass
+ *        the buffer with the same number as `send` (the receiver reads it from its predecessor's memory)
+ *  rfa_peer_destroy(handle)             unmaps, frees the buffers; call it on every rank before a neighbour exits
+ * A rank that never posts leaves its neighbours' transport streams waiting (as a missing rank does to an NCCL ring).
+ * Host pointers: handle, out, prev, next, ptr.
+ */
+size_t rfa_peer_export_bytes(void);
+int rfa_peer_create(int rank, int world, void** handle);
+int rfa_peer_alloc(void* handle, size_t bytes, void** dev_ptr);
+int rfa_peer_export(void* handle, void* out, size_t cap);
+int rfa_peer_connect(void* handle, const void* prev_blob, const void* next_blob);
+int rfa_peer_destroy(void* handle);
+int rfa_peer_post(void* handle, const void* send, void* recv, size_t bytes, void* compute_stream);
+int rfa_peer_wait(void* handle, int slot, void* compute_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -33,6 +33,9 @@ int rfa_debug_set_trace(unsigned long long* buf, int n_ctas, int cap);
  */
 int rfa_debug_ring_timing(void* handle, int on);
 int rfa_debug_ring_elapsed(void* handle, int slot, float* ms);
+/* The same for a peer-memory transport handle (rfa_peer_create). */
+int rfa_debug_peer_timing(void* handle, int on);
+int rfa_debug_peer_elapsed(void* handle, int slot, float* ms);
 
 #ifdef __cplusplus
 }

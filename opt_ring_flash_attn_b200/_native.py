@@ -57,6 +57,16 @@ SIGNATURES = {
     "rfa_comm_destroy": (_i, [_vp]),
     "rfa_ring_post": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "rfa_ring_wait": (_i, [_vp, _i, _vp]),
+    "rfa_peer_export_bytes": (_sz, []),
+    "rfa_peer_create": (_i, [_i, _i, ctypes.POINTER(ctypes.c_void_p)]),
+    "rfa_peer_alloc": (_i, [_vp, _sz, ctypes.POINTER(ctypes.c_void_p)]),
+    "rfa_peer_export": (_i, [_vp, _vp, _sz]),
+    "rfa_peer_connect": (_i, [_vp, _vp, _vp]),
+    "rfa_peer_destroy": (_i, [_vp]),
+    "rfa_peer_post": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "rfa_peer_wait": (_i, [_vp, _i, _vp]),
+    "rfa_debug_peer_timing": (_i, [_vp, _i]),
+    "rfa_debug_peer_elapsed": (_i, [_vp, _i, ctypes.POINTER(ctypes.c_float)]),
     "rfa_debug_mma_probe": (_i, [_i, _vp, _vp, _vp, _vp, _vp]),
     "rfa_debug_set_trace": (_i, [_vp, _i, _i]),
     "rfa_debug_ring_timing": (_i, [_vp, _i]),
@@ -285,6 +295,58 @@ def ring_post(handle: int, send: torch.Tensor, recv: torch.Tensor, stream=None) 
 def ring_wait(handle: int, slot: int, stream=None, device: Optional[torch.device] = None) -> None:
     s = stream.cuda_stream if stream is not None else torch.cuda.current_stream(device).cuda_stream
     _check(load().rfa_ring_wait(handle, slot, s), "rfa_ring_wait", kernels=0)
+
+
+def peer_create(rank: int, world: int) -> int:
+    handle = ctypes.c_void_p()
+    _check(load().rfa_peer_create(rank, world, ctypes.byref(handle)), "rfa_peer_create", kernels=0)
+    return handle.value
+
+
+def peer_alloc(handle: int, nbytes: int) -> int:
+    ptr = ctypes.c_void_p()
+    _check(load().rfa_peer_alloc(handle, nbytes, ctypes.byref(ptr)), "rfa_peer_alloc", kernels=0)
+    return ptr.value
+
+
+def peer_export(handle: int) -> bytes:
+    n = load().rfa_peer_export_bytes()
+    buf = ctypes.create_string_buffer(n)
+    _check(load().rfa_peer_export(handle, buf, n), "rfa_peer_export", kernels=0)
+    return buf.raw
+
+
+def peer_connect(handle: int, prev_blob: bytes, next_blob: bytes) -> None:
+    _check(load().rfa_peer_connect(handle, ctypes.c_char_p(prev_blob), ctypes.c_char_p(next_blob)), "rfa_peer_connect",
+           kernels=0)
+
+
+def peer_destroy(handle: int) -> None:
+    _check(load().rfa_peer_destroy(handle), "rfa_peer_destroy", kernels=0)
+
+
+def peer_post(handle: int, send: torch.Tensor, recv: torch.Tensor, stream=None) -> int:
+    nbytes = send.numel() * send.element_size()
+    with _on_device(send):
+        slot = load().rfa_peer_post(handle, _ptr(send), _ptr(recv), nbytes, _stream(stream, send))
+    if slot < 0:
+        _check(slot, "rfa_peer_post", kernels=0)
+    return slot
+
+
+def peer_wait(handle: int, slot: int, stream=None, device: Optional[torch.device] = None) -> None:
+    s = stream.cuda_stream if stream is not None else torch.cuda.current_stream(device).cuda_stream
+    _check(load().rfa_peer_wait(handle, slot, s), "rfa_peer_wait", kernels=0)
+
+
+def peer_timing(handle: int, on: bool) -> None:
+    _check(load().rfa_debug_peer_timing(handle, int(on)), "rfa_debug_peer_timing", kernels=0)
+
+
+def peer_elapsed_ms(handle: int, slot: int) -> float:
+    ms = ctypes.c_float()
+    _check(load().rfa_debug_peer_elapsed(handle, slot, ctypes.byref(ms)), "rfa_debug_peer_elapsed", kernels=0)
+    return float(ms.value)
 
 
 def ring_timing(handle: int, on: bool) -> None:

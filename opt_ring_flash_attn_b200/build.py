@@ -21,7 +21,7 @@ LIB_NAME = "librfa_b200.so"
 LIB_PATH = PKG_DIR / LIB_NAME
 OBJ_DIR = PKG_DIR / "build"
 
-SOURCES = ["aux.cu", "fwd_hop.cu", "bwd_hop.cu", "probe.cu", "noalloc.cu", "comm.cu"]
+SOURCES = ["aux.cu", "fwd_hop.cu", "bwd_hop.cu", "probe.cu", "noalloc.cu", "comm.cu", "peer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

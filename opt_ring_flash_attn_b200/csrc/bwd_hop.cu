@@ -28,10 +28,6 @@
 #include "common.h"
 #include "tc05.cuh"
 
-#ifndef RFA_BWD_FRAG16
-#define RFA_BWD_FRAG16 1
-#endif
-
 namespace rfa {
 
 // Pause (ns) a reduction warp takes after each vector reduction.  An SM can push 32 B per clock towards the L2, so
@@ -377,115 +373,6 @@ __global__ void __launch_bounds__(640, 1)
     const Exp2Poly exp2_poly;
     const uint64_t nscale2 = pack_f2(-p.scale_log2, -p.scale_log2);
     bool ok = run;
-#if RFA_BWD_FRAG16
-    // Fragment form of the two elementwise phases: the tile is read with the 16-lane tensor-memory shape, so a thread
-    // holds 4 kv rows x (BQ/8) query columns instead of 1 row x BQ/2 columns.  The per-column statistics (lse2, delta)
-    // are the expensive operand here -- every one is a shared-memory broadcast, and those loads were a third of the
-    // shared-memory pipe's load next to the tensor cores' operand reads -- and this way a thread needs a quarter of them.
-    constexpr int NX = kHalfCols / 8;  // groups of 8 columns per group of warps: 8 (BQ = 128) or 4 (BQ = 64)
-    const int t4 = lane & 3;
-    const int r8 = lane >> 2;
-    int mlim[2][2];
-#pragma unroll
-    for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int kvp = n0 + quarter * 32 + hh * 16 + u * 8 + r8;
-        mlim[hh][u] = (kvp >= p.kv_len) ? 0x7fffffff : (p.causal ? kvp : static_cast<int>(0x80000000));
-      }
-    const uint32_t half_lanes = 16u << 16;
-    for (int t = 0; t < T_total && ok; ++t) {
-      const int st = t % NST;
-      const int i = q_tile(t);
-      const float* lse2_s = reinterpret_cast<const float*>(stat_ptr + st * Cfg::kStatBytes) + col0 + 2 * t4;
-      const float* delta_s = lse2_s + BQ;
-      if (!mbar_wait_warp(&bar_q_full[st], (t / NST) & 1, abort_p)) { ok = false; break; }
-      tr.mark(19);
-      if (!mbar_wait_warp(&bar_s_full, t & 1, abort_p)) { ok = false; break; }
-      tr.mark(20);
-      tc_fence_after_sync();
-      const int q0 = i * BQ + col0 + 2 * t4;
-      const bool masked = (p.causal && (i * BQ < n0 + 127)) || (n0 + 128 > p.kv_len);
-      uint32_t pk[2][2 * NX];
-      {
-        uint32_t r[2][4 * NX];
-        tmem_ld_frag(a_s, r[0]);
-        tmem_ld_frag(a_s + half_lanes, r[1]);
-        tmem_ld_wait_frag(r[0], r[1]);
-        tr.mark(21);
-        // P^T = exp2(scale*log2e * S^T - lse2[q]); masked only on diagonal tiles and on a tile that straddles kv_len.
-        auto p_phase = [&](auto mask_tag) {
-          constexpr bool kMask = decltype(mask_tag)::value;
-#pragma unroll
-          for (int j = 0; j < NX; ++j) {
-            const float2 l2 = *reinterpret_cast<const float2*>(lse2_s + 8 * j);
-            const uint64_t lp = pack_f2(l2.x, l2.y);
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-              for (int u = 0; u < 2; ++u) {
-                float y0, y1;
-                unpack_f2(fma2(pack_u2(r[hh][4 * j + 2 * u], r[hh][4 * j + 2 * u + 1]), nscale2, lp), y0, y1);
-                float e0 = fast_exp2(-y0);
-                float e1 = fast_exp2(-y1);
-                if (kMask) {
-                  if (q0 + 8 * j < mlim[hh][u]) e0 = 0.f;
-                  if (q0 + 8 * j + 1 < mlim[hh][u]) e1 = 0.f;
-                }
-                pk[hh][2 * j + u] = Pack2<T>::pack(e0, e1);
-              }
-          }
-        };
-        if (masked) p_phase(std::true_type{});
-        else p_phase(std::false_type{});
-      }
-      tr.mark(26);
-      // P^T (16 bit, two per column) goes over the start of this group's own S^T columns.
-      tmem_st_frag(a_s, pk[0]);
-      tmem_st_frag(a_s + half_lanes, pk[1]);
-      tmem_st_wait();
-      tr.mark(27);
-      tc_fence_before_sync();
-      mbar_arrive(&bar_p_ready);
-      tr.mark(22);
-
-      if (!mbar_wait_warp(&bar_dp_full, t & 1, abort_p)) { ok = false; break; }
-      tr.mark(23);
-      tc_fence_after_sync();
-      {
-        uint32_t r[2][4 * NX];
-        tmem_ld_frag(a_dp, r[0]);
-        tmem_ld_frag(a_dp + half_lanes, r[1]);
-        tmem_ld_wait_frag(r[0], r[1]);
-        tr.mark(24);
-#pragma unroll
-        for (int j = 0; j < NX; ++j) {
-          const float2 d2 = *reinterpret_cast<const float2*>(delta_s + 8 * j);
-          const uint64_t dp2 = pack_f2(d2.x, d2.y);
-          // the pair of columns col0 + 8j + 2*t4, +1 = 4 bytes inside 16-byte chunk (col0 + 8j) / 8 of its panel
-          const int colg = col0 + 8 * j;
-          uint8_t* chunk_base = ds_ptr + (colg / 64) * kPanelK + 4 * t4;
-          const int chunk = (colg % 64) / 8;
-#pragma unroll
-          for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const float2 pf = Pack2<T>::unpack(pk[hh][2 * j + u]);
-              float s0, s1;
-              unpack_f2(mul2(pack_f2(pf.x, pf.y),
-                             sub2(pack_u2(r[hh][4 * j + 2 * u], r[hh][4 * j + 2 * u + 1]), dp2)), s0, s1);
-              const int rr = quarter * 32 + hh * 16 + u * 8 + r8;
-              *reinterpret_cast<uint32_t*>(chunk_base + sw128_offset(rr, chunk)) = Pack2<T>::pack(s0, s1);
-            }
-        }
-      }
-      tr.mark(28);
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      mbar_arrive(&bar_ds_ready);
-      tr.mark(25);
-    }
-#else
     for (int t = 0; t < T_total && ok; ++t) {
       const int st = t % NST;
       const int i = q_tile(t);
@@ -605,7 +492,6 @@ __global__ void __launch_bounds__(640, 1)
       mbar_arrive(&bar_ds_ready);
       tr.mark(25);
     }
-#endif
     // ---- epilogue: group 0 writes dV, group 1 writes dK (scaled) ----
     if (ok) ok = mbar_wait_warp(&bar_final, 0, abort_p);
     if (ok) {

@@ -507,59 +507,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 __device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" : RFA_RW8(r, 0), RFA_RW8(r, 8) : : "memory");
 }
-// 16-lane shapes.  A warp addresses 16 lanes (taddr's lane field selects which 16 of its 32) and each thread gets a
-// fragment like an mma accumulator's: with t4 = lane % 4 and r8 = lane / 4,
-//   16x256b.xN load : reg[4j+0..1] = (row r8,     columns 8j + 2*t4, +1),  reg[4j+2..3] = (row r8 + 8, same columns)
-//   16x128b.xN store: reg[2j]      = (row r8,     column  4j + t4),        reg[2j+1]    = (row r8 + 8, same column)
-// so a thread sees 2 rows x 2N columns instead of 1 row x 32 columns: per-column operands (statistics of a query
-// column) are needed for a quarter of the columns only.  The pair (column 2c, 2c+1) of the load fragment packs into
-// 16-bit cell c of the store fragment, which is how a tile goes from fp32 scores to a 16-bit MMA operand in place.
-__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : RFA_R8(r, 0), RFA_R8(r, 8), RFA_R8(r, 16), RFA_R8(r, 24)
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : RFA_R8(r, 0), RFA_R8(r, 8)
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.16x128b.x8.b32 [%16], "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
-      :
-      : RFA_I8(r, 0), RFA_I8(r, 8), "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_16x128b_x4(uint32_t taddr, const uint32_t (&r)[8]) {
-  asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
-               :
-               : RFA_I8(r, 0), "r"(taddr)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld_frag(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld_16x256b_x8(taddr, r); }
-__device__ __forceinline__ void tmem_ld_frag(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_16x256b_x4(taddr, r); }
-__device__ __forceinline__ void tmem_st_frag(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st_16x128b_x8(taddr, r); }
-__device__ __forceinline__ void tmem_st_frag(uint32_t taddr, const uint32_t (&r)[8]) { tmem_st_16x128b_x4(taddr, r); }
-__device__ __forceinline__ void reg_fence16(uint32_t (&r)[16]) {
-  asm volatile("" : RFA_RW8(r, 0), RFA_RW8(r, 8) : : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait_frag(uint32_t (&a)[32], uint32_t (&b)[32]) {
-  tmem_ld_wait32(a);
-  reg_fence32(b);
-}
-__device__ __forceinline__ void tmem_ld_wait_frag(uint32_t (&a)[16], uint32_t (&b)[16]) {
-  tmem_ld_wait16(a);
-  reg_fence16(b);
-}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ----------------------------------------------------------------------------

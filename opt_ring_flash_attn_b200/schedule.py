@@ -26,7 +26,7 @@ import torch
 import torch.distributed as dist
 
 from . import _native, workspace
-from .transport import make_transport
+from .transport import PeerRingTransport, make_transport, transport_mode
 
 
 # (ring key, device, ring name) -> transport.  The key is the process-group object itself (not its id(), which
@@ -60,9 +60,23 @@ def _transport(group, device: torch.device, tag: str):
     return t
 
 
+def _ring_factory(group, device: torch.device):
+    """``ring(name, sizes) -> (transport, uint8 buffers)`` for the workspaces: the peer-memory transport brings its
+    own buffers (one transport per ring and workspace, created collectively); the others are cached per ring and
+    work on plain tensors."""
+    def ring(tag: str, sizes):
+        if not _is_ring_handle(group) and transport_mode(group, device) == "peer":
+            comm = PeerRingTransport(group, device, sizes)
+            return comm, comm.buffers
+        return _transport(group, device, tag), [torch.empty(n, dtype=torch.uint8, device=device) for n in sizes]
+    return ring
+
+
 def shutdown() -> None:
-    """Destroy every cached transport (NCCL communicators, streams, events).  Call it before destroying the
-    process group the transports were created on; it also runs at interpreter exit."""
+    """Destroy every transport (mapped peer memory, NCCL communicators, streams, events) and the scratch that
+    belongs to them.  Call it on every rank before destroying the process group the transports were created on; it
+    also runs at interpreter exit."""
+    workspace.clear()
     for t in list(_transports.values()):
         try:
             t.close()
@@ -115,7 +129,7 @@ def ring_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softm
     W, rank = _world(group)
     B, S, Hq, D = q.shape
     _agree_on_shapes(group, q, k, W)
-    ws = workspace.forward_workspace(q, k, W, owner=_ws_owner(group))
+    ws = workspace.forward_workspace(q, k, W, owner=_ws_owner(group), ring=_ring_factory(group, q.device))
     workspace.raise_if_failed(ws, "ring_flash_attn forward")
     out = torch.empty_like(q)
     lse = torch.empty(B, Hq, _native.padded_seq(S), dtype=torch.float32, device=q.device)
@@ -125,7 +139,7 @@ def ring_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softm
         workspace.publish_status(ws, "ring_flash_attn forward")
         return out, lse
 
-    comm = _transport(group, q.device, "fwd_kv")
+    comm = ws.comms["fwd_kv"]
     kn.pack_kv(k, v, ws.kv_send)
     cur = ws.kv_send
     k_cur, v_cur = k, v
@@ -180,7 +194,8 @@ def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
     optimized_ring_flash_attn.py:730-735) at some cost in speed."""
     kn = kernels if kernels is not None else _native
     W, rank = _world(group)
-    ws = workspace.backward_workspace(q, k, W, backward_comm_dtype(q.dtype), owner=_ws_owner(group))
+    ws = workspace.backward_workspace(q, k, W, backward_comm_dtype(q.dtype), owner=_ws_owner(group),
+                                      ring=_ring_factory(group, q.device))
     workspace.raise_if_failed(ws, "ring_flash_attn backward")
     wire16 = ws.dkdv[0].dtype != torch.float32
     order = {"dq_order": ws.dq_order} if deterministic else {}
@@ -201,8 +216,7 @@ def ring_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v
         workspace.publish_status(ws, "ring_flash_attn backward")
         return dq, dk, dv
 
-    kv_comm = _transport(group, q.device, "bwd_kv")
-    dkv_comm = _transport(group, q.device, "bwd_dkdv")
+    kv_comm, dkv_comm = ws.comms["bwd_kv"], ws.comms["bwd_dkdv"]
     kn.pack_kv(k, v, ws.kv_send)
     cur = ws.kv_send
     k_cur, v_cur = k, v
@@ -257,7 +271,7 @@ def zigzag_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sof
     W, rank = _world(group)
     B, S, Hq, D = q.shape
     _agree_on_shapes(group, q, k, W)
-    ws = workspace.forward_workspace(q, k, W, owner=_ws_owner(group))
+    ws = workspace.forward_workspace(q, k, W, owner=_ws_owner(group), ring=_ring_factory(group, q.device))
     workspace.raise_if_failed(ws, "ring_flash_attn forward")
     out = torch.empty_like(q)
     lse = torch.empty(B, Hq, _native.padded_seq(S), dtype=torch.float32, device=q.device)
@@ -266,7 +280,7 @@ def zigzag_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sof
         workspace.publish_status(ws, "ring_flash_attn forward")
         return out, lse
     half = _zigzag_half(S)
-    comm = _transport(group, q.device, "fwd_kv")
+    comm = ws.comms["fwd_kv"]
     kn.pack_kv(k, v, ws.kv_send)
     cur = ws.kv_send
     k_cur, v_cur = k, v
@@ -304,7 +318,8 @@ def zigzag_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
                              deterministic=deterministic)
     S = q.shape[1]
     half = _zigzag_half(S)
-    ws = workspace.backward_workspace(q, k, W, backward_comm_dtype(q.dtype), owner=_ws_owner(group))
+    ws = workspace.backward_workspace(q, k, W, backward_comm_dtype(q.dtype), owner=_ws_owner(group),
+                                      ring=_ring_factory(group, q.device))
     workspace.raise_if_failed(ws, "ring_flash_attn backward")
     order = {"dq_order": ws.dq_order} if deterministic else {}
     wire16 = ws.dkdv[0].dtype != torch.float32
@@ -313,8 +328,7 @@ def zigzag_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
     dq = torch.empty_like(q)
     dk = torch.empty_like(k)
     dv = torch.empty_like(v)
-    kv_comm = _transport(group, q.device, "bwd_kv")
-    dkv_comm = _transport(group, q.device, "bwd_dkdv")
+    kv_comm, dkv_comm = ws.comms["bwd_kv"], ws.comms["bwd_dkdv"]
     kn.pack_kv(k, v, ws.kv_send)
     cur = ws.kv_send
     k_cur, v_cur = k, v

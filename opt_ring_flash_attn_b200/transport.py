@@ -140,13 +140,110 @@ class NativeRingTransport:
             with torch.cuda.device(self.device):
                 self._native.comm_destroy(handle)
 
+    # diagnostics: device time of each transfer (see rfa_b200_debug.h)
+    def set_timing(self, on: bool) -> None:
+        self._native.ring_timing(self._handle, on)
 
-def make_transport(group: Optional[dist.ProcessGroup], device: torch.device):
-    """Native NCCL transport for CUDA tensors on an NCCL group; the process-group transport otherwise
-    (CPU ranks on gloo in the tests) or when RFA_B200_TRANSPORT=torch."""
+    def elapsed_ms(self, slot: int) -> float:
+        return self._native.ring_elapsed_ms(self._handle, slot)
+
+    def last_slot(self) -> int:
+        return self._pending[-1]
+
+
+class _DeviceMemory:
+    """Lets torch wrap device memory that the transport library owns (``__cuda_array_interface__``)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerRingTransport:
+    """Same protocol over peer memory (``rfa_peer_*``): every transfer is a copy-engine copy out of the previous
+    rank's buffer, ordered by flags in device memory; no SM takes part, so transfers neither wait for thread-block
+    slots behind a hop kernel nor take SMs away from it.  The ring buffers belong to the transport (they must be
+    exportable to the neighbours): ``buffers[i]`` are uint8 tensors over them, allocated for the sizes given at
+    construction, in the same order on every rank.  Construction is collective over the group."""
+
+    owns_buffers = True
+
+    def __init__(self, group: Optional[dist.ProcessGroup], device: torch.device, sizes: List[int]):
+        from . import _native
+
+        self._native = _native
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world_size = dist.get_world_size(group)
+        self.device = device
+        self._handle = None
+        with torch.cuda.device(device):
+            self._handle = _native.peer_create(self.rank, self.world_size)
+            ptrs = [_native.peer_alloc(self._handle, int(n)) for n in sizes]
+            blob = _native.peer_export(self._handle)
+        blobs = [None] * self.world_size
+        dist.all_gather_object(blobs, blob, group=group)
+        with torch.cuda.device(device):
+            _native.peer_connect(self._handle, blobs[(self.rank - 1) % self.world_size],
+                                 blobs[(self.rank + 1) % self.world_size])
+        self.buffers = [torch.as_tensor(_DeviceMemory(p, int(n)), device=device) for p, n in zip(ptrs, sizes)]
+        dist.barrier(group=group)  # every rank has mapped its neighbours before anyone posts
+        self._pending: Deque[int] = deque()
+        self.posted = 0
+        self.bytes_sent = 0
+
+    def post(self, send_buf: torch.Tensor, recv_buf: torch.Tensor) -> None:
+        if send_buf.data_ptr() == recv_buf.data_ptr():
+            raise RuntimeError("ring transport: send and receive buffers must differ")
+        if len(self._pending) >= 6:
+            raise RuntimeError("ring transport: too many transfers outstanding")
+        self._pending.append(self._native.peer_post(self._handle, send_buf, recv_buf))
+        self.posted += 1
+        self.bytes_sent += send_buf.numel() * send_buf.element_size()
+
+    def wait(self) -> None:
+        if not self._pending:
+            raise RuntimeError("ring transport: wait() without a posted transfer")
+        self._native.peer_wait(self._handle, self._pending.popleft(), device=self.device)
+
+    def drain(self) -> None:
+        while self._pending:
+            self.wait()
+
+    def close(self) -> None:
+        """Unmaps the neighbours' memory and frees the ring buffers.  The tensors in ``buffers`` die with it.
+        Every rank must close before a neighbour's process exits (the mappings point into its memory)."""
+        if self._handle is not None:
+            handle, self._handle = self._handle, None
+            self._pending.clear()
+            self.buffers = []
+            with torch.cuda.device(self.device):
+                torch.cuda.synchronize(self.device)
+                self._native.peer_destroy(handle)
+
+    def set_timing(self, on: bool) -> None:
+        self._native.peer_timing(self._handle, on)
+
+    def elapsed_ms(self, slot: int) -> float:
+        return self._native.peer_elapsed_ms(self._handle, slot)
+
+    def last_slot(self) -> int:
+        return self._pending[-1]
+
+
+def transport_mode(group: Optional[dist.ProcessGroup], device: torch.device) -> str:
+    """``peer`` (copy engines over mapped peer memory), ``native`` (private NCCL communicator) or ``torch`` (the
+    process group's own send/recv).  CUDA ranks on an NCCL group default to ``peer``; ``RFA_B200_TRANSPORT``
+    overrides; everything else (CPU ranks on gloo in the tests) uses ``torch``."""
     import os
 
-    if (device.type == "cuda" and dist.get_backend(group) == "nccl"
-            and os.environ.get("RFA_B200_TRANSPORT", "native") != "torch"):
+    if device.type != "cuda" or dist.get_backend(group) != "nccl":
+        return "torch"
+    mode = os.environ.get("RFA_B200_TRANSPORT", "peer")
+    return mode if mode in ("peer", "native", "torch") else "peer"
+
+
+def make_transport(group: Optional[dist.ProcessGroup], device: torch.device):
+    """A transport that works on caller-owned buffers: NCCL (``native``) or the process group (``torch``)."""
+    if transport_mode(group, device) in ("peer", "native"):
         return NativeRingTransport(group, device)
     return RingTransport(group, device)

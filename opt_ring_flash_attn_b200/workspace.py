@@ -42,6 +42,7 @@ class ForwardWorkspace:
     status: torch.Tensor              # int32 [1]
     status_host: Optional[torch.Tensor] = None   # pinned int32 [1]: last published copy of ``status``
     status_event: Any = None                     # recorded after the copy into status_host
+    comms: Dict[str, Any] = field(default_factory=dict)  # ring name -> transport the ring buffers belong to
 
 
 @dataclass
@@ -57,6 +58,7 @@ class BackwardWorkspace:
     dq_order: Optional[torch.Tensor] = None      # int32 counters of the ordered (deterministic) dQ reductions
     status_host: Optional[torch.Tensor] = None
     status_event: Any = None
+    comms: Dict[str, Any] = field(default_factory=dict)
 
 
 # owner -> (key, workspace): one slot per owner (None = the process's own rank; a ring handle brings its own key)
@@ -72,6 +74,28 @@ def _new_status(dev: torch.device):
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     host = torch.zeros(1, dtype=torch.int32, pin_memory=True) if dev.type == "cuda" else None
     return status, host
+
+
+def _ring_buffers(ring, tag: str, n: int, shape, dtype: torch.dtype, dev: torch.device):
+    """``n`` packed ring buffers of ``shape``/``dtype`` and the transport they travel on.  ``ring(tag, sizes)``
+    (given by the schedules) returns ``(transport, uint8 buffers)``: a peer-memory transport owns its buffers, the
+    others take plain tensors.  Without a factory the buffers are plain tensors and no transport is attached."""
+    nbytes = torch.empty(0, dtype=dtype).element_size()
+    for d in shape:
+        nbytes *= d
+    if ring is None:
+        return None, [torch.empty(shape, dtype=dtype, device=dev) for _ in range(n)]
+    comm, raw = ring(tag, [nbytes] * n)
+    return comm, [b.view(dtype).view(shape) for b in raw]
+
+
+def _retire(ws) -> None:
+    """A workspace leaves the cache: transports that own its ring buffers go with it (collective-free; every rank
+    replaces its workspace at the same call, so neighbours unmap each other at the same point of the program)."""
+    for comm in ws.comms.values():
+        if comm is not None and getattr(comm, "owns_buffers", False):
+            comm.close()
+    ws.comms.clear()
 
 
 def all_workspaces() -> List:
@@ -122,11 +146,13 @@ def check_all(what: str = "ring_flash_attn") -> None:
             _fail(ws, code, what)
 
 
-def forward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int, owner=None) -> ForwardWorkspace:
+def forward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int, owner=None, ring=None) -> ForwardWorkspace:
     key = _key(q, k, world_size)
     hit = _fwd_cache.get(owner)
     if hit is not None and hit[0] == key:
         return hit[1]
+    if hit is not None:
+        _retire(hit[1])
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
     dev = q.device
@@ -138,15 +164,14 @@ def forward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int, owner=N
         acc = torch.empty(B * Hq * spad * _padded_head_dim(D), dtype=torch.float32, device=dev)
         m = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
         l = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
-        kv_send = torch.empty(2, B, S, Hkv, D, dtype=q.dtype, device=dev)
-        kv_recv = [torch.empty_like(kv_send) for _ in range(2)]
-        ws = ForwardWorkspace(acc, m, l, kv_send, kv_recv, status, status_host)
+        comm, kv = _ring_buffers(ring, "fwd_kv", 3, (2, B, S, Hkv, D), q.dtype, dev)
+        ws = ForwardWorkspace(acc, m, l, kv[0], kv[1:], status, status_host, comms={"fwd_kv": comm})
     _fwd_cache[owner] = (key, ws)  # single slot per owner, like the reference
     return ws
 
 
 def backward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int,
-                       comm_dtype: torch.dtype = torch.float32, owner=None) -> BackwardWorkspace:
+                       comm_dtype: torch.dtype = torch.float32, owner=None, ring=None) -> BackwardWorkspace:
     """``comm_dtype`` is the dtype of the travelling dK/dV buffers (fp32, or the input dtype for 16-bit transport,
     optimized_ring_flash_attn.py:205-208, 271-272); this hop's own block is always fp32."""
     if world_size == 1:
@@ -155,6 +180,8 @@ def backward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int,
     hit = _bwd_cache.get(owner)
     if hit is not None and hit[0] == key:
         return hit[1]
+    if hit is not None:
+        _retire(hit[1])
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
     dev = q.device
@@ -162,22 +189,26 @@ def backward_workspace(q: torch.Tensor, k: torch.Tensor, world_size: int,
     delta = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
     lse2 = torch.empty(B, Hq, spad, dtype=torch.float32, device=dev)
     dq_acc = torch.empty(B * Hq * spad * _padded_head_dim(D), dtype=torch.float32, device=dev)
-    nslots = 1 if world_size == 1 else 2
-    dkdv = [torch.empty(2, B, S, Hkv, D, dtype=comm_dtype, device=dev) for _ in range(nslots)]
+    comms = {}
     if world_size == 1:
+        dkdv = [torch.empty(2, B, S, Hkv, D, dtype=comm_dtype, device=dev)]
         kv_send, kv_recv, block_dkdv = None, [], None
     else:
-        kv_send = torch.empty(2, B, S, Hkv, D, dtype=q.dtype, device=dev)
-        kv_recv = [torch.empty_like(kv_send) for _ in range(2)]
+        comms["bwd_dkdv"], dkdv = _ring_buffers(ring, "bwd_dkdv", 2, (2, B, S, Hkv, D), comm_dtype, dev)
+        comms["bwd_kv"], kv = _ring_buffers(ring, "bwd_kv", 3, (2, B, S, Hkv, D), q.dtype, dev)
+        kv_send, kv_recv = kv[0], kv[1:]
         block_dkdv = torch.empty(2, B, S, Hkv, D, dtype=torch.float32, device=dev)
     status, status_host = _new_status(dev)
     # counters of the ordered dQ reductions: 8 per (batch, head, query tile of 64 rows) covers every head dim
     dq_order = torch.zeros(B * Hq * ((S + 63) // 64) * 2 * 8, dtype=torch.int32, device=dev)
-    ws = BackwardWorkspace(delta, lse2, dq_acc, dkdv, block_dkdv, kv_send, kv_recv, status, dq_order, status_host)
+    ws = BackwardWorkspace(delta, lse2, dq_acc, dkdv, block_dkdv, kv_send, kv_recv, status, dq_order, status_host,
+                           comms=comms)
     _bwd_cache[owner] = (key, ws)
     return ws
 
 
 def clear() -> None:
+    for ws in all_workspaces():
+        _retire(ws)
     _fwd_cache.clear()
     _bwd_cache.clear()

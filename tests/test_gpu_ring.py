@@ -1,4 +1,5 @@
-"""The real multi-process path: one process per GPU, NCCL ring, public operator, compared with the oracle.
+"""The real multi-process path: one process per GPU, public operator, both GPU transports (copy engines over mapped
+peer memory, and the private NCCL communicator), compared with the oracle.
 Skipped when fewer than two GPUs are visible (the single-GPU emulation in test_gpu_kernels.py covers the kernels)."""
 import os
 import socket
@@ -15,7 +16,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, cfg, errs):
+def _worker(rank, world, port, cfg, errs, transport):
     import torch.distributed as dist
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -31,6 +32,7 @@ def _worker(rank, world, port, cfg, errs):
         from oracle.ring_attn_oracle import zigzag_oracle, zigzag_shard
 
         B, S, Hq, Hkv, D, causal, dtype = cfg[:7]
+        os.environ["RFA_B200_TRANSPORT"] = transport
         zigzag = len(cfg) > 7 and cfg[7]
         wire16 = len(cfg) > 8 and cfg[8]  # dK/dV travel in the input dtype (the reference's OPTIMIZED_RING_BWD_COMM_BF16)
         os.environ["OPTIMIZED_RING_BWD_COMM_BF16"] = "1" if wire16 else "0"
@@ -63,6 +65,9 @@ def _worker(rank, world, port, cfg, errs):
         assert rel(kl.grad, ref["dk"][rank]) <= 2e-2
         assert rel(vl.grad, ref["dv"][rank]) <= 2e-2
         dist.barrier()
+        from opt_ring_flash_attn_b200 import schedule
+        schedule.shutdown()  # unmap the neighbours' memory before any of them exits
+        dist.barrier()
     except Exception as e:
         errs.put(f"rank {rank}: {type(e).__name__}: {e}")
         raise
@@ -78,7 +83,8 @@ def _worker(rank, world, port, cfg, errs):
     (1, 512, 4, 2, 128, True, torch.bfloat16, True),  # zigzag layout
     (1, 384, 4, 2, 128, True, torch.bfloat16, False, True),  # 16-bit dK/dV transport
 ])
-def test_ring_nccl(cfg):
+@pytest.mark.parametrize("transport", ["peer", "native"])
+def test_ring_nccl(cfg, transport):
     import torch.multiprocessing as mp
 
     world = min(torch.cuda.device_count(), 4)
@@ -87,11 +93,11 @@ def test_ring_nccl(cfg):
     ctx = mp.get_context("spawn")
     errs = ctx.SimpleQueue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, cfg, errs)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, cfg, errs, transport)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
-        p.join(300)
+        p.join(150)
     msgs = []
     while not errs.empty():
         msgs.append(errs.get())
