@@ -528,6 +528,60 @@ def grid_mode(args, dist, dev, rank, world):
                           "over ranks; bf16, causal, MHA, B=1", "rows": rows}), flush=True)
 
 
+def aux_mode(args, cfg, dev):
+    """The bandwidth-bound kernels of the path at the workload's buffer sizes, alone: CUDA-event time and achieved
+    HBM rate (algorithmic bytes / time) against the measured copy rate."""
+    from opt_ring_flash_attn_b200 import _native
+
+    B, S, Hq, Hkv, D, scale, std, seed, desc = cfg
+    peaks, peak_kind = load_peaks()
+    hbm = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    q, k, v, dout = make_shard(cfg, 0, dev)
+    spad = _native.padded_seq(S)
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.randn_like(q)
+    lse = torch.randn(B, Hq, spad, device=dev)
+    delta, lse2 = torch.empty_like(lse), torch.empty_like(lse)
+    dq_acc = torch.randn(_native.dq_acc_elems(B, S, Hq, D), device=dev)
+    dq = torch.empty_like(q)
+    a32 = torch.randn(2, B, S, Hkv, D, device=dev)
+    b32 = torch.randn_like(a32)
+    a16 = a32.to(q.dtype)
+    dk = torch.empty_like(k)
+    kv = torch.empty(2, B, S, Hkv, D, dtype=q.dtype, device=dev)
+    flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device=dev)
+    e = q.element_size()
+    n_q, n_kv = q.numel(), a32.numel()
+    cases = [
+        ("bwd_prepare (delta, lse2, accumulator cleared)", lambda: _native.bwd_prepare(out, dout, lse, delta, lse2, dq_acc, st),
+         2 * n_q * e + 3 * lse.numel() * 4 + dq_acc.numel() * 4),
+        ("dq_finalize (fp32 tiled accumulator -> dq)", lambda: _native.dq_finalize(dq_acc, dq), dq_acc.numel() * 4 + n_q * e),
+        ("dkdv_accumulate (fp32 ring accumulate)", lambda: _native.dkdv_accumulate(a32, b32, a32), 3 * n_kv * 4),
+        ("dkdv_accumulate_to16 (16-bit ring accumulate)", lambda: _native.dkdv_accumulate_to16(a16, b32, a16), n_kv * (4 + 2 * e)),
+        ("cast_from_f32 (dK or dV)", lambda: _native.cast_from_f32(a32[0], dk), dk.numel() * (4 + e)),
+        ("pack_kv (two device copies)", lambda: _native.pack_kv(k, v, kv), 2 * kv.numel() * e),
+    ]
+    rows = []
+    for name, fn, nbytes in cases:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for i in range(10):
+            flush.fill_(i)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ms = statistics.median(ts)
+        rows.append({"kernel": name, "ms": round(ms, 4), "algorithmic_mb": round(nbytes / 1e6, 1),
+                     "gb_s": round(nbytes / ms / 1e6, 1), "frac_of_hbm_peak": round(nbytes / ms / 1e6 / hbm, 3)})
+    print(json.dumps({"aux_kernels": rows, "workload": f"{args.config}: {desc}", "hbm_peak_gb_s": hbm, "peak_kind": peak_kind,
+                      "l2": "L2 flushed (256 MiB write) before every timed launch"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -544,6 +598,7 @@ def main():
                     help="zigzag layout (rank r holds chunks r and 2W-1-r) as the timed step; not the headline config")
     ap.add_argument("--hops", action="store_true", help="add the per-hop timeline of the slowest rank")
     ap.add_argument("--grid", default=None, choices=["speedup", "ablation"])
+    ap.add_argument("--aux", action="store_true", help="time the bandwidth-bound kernels alone (1 GPU) and exit")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     B, S, Hq, Hkv, D, scale, std, seed, desc = cfg
@@ -568,6 +623,10 @@ def main():
     _native.load()
     group = dist.group.WORLD if world > 1 else None
 
+    if args.aux:
+        aux_mode(args, cfg, dev)
+        return
+
     if args.grid:
         grid_mode(args, dist, dev, rank, world)
         if world > 1:
@@ -576,7 +635,8 @@ def main():
             dist.destroy_process_group()
         return
 
-    warmup = max(args.warmup, 3)
+    # at least three warm-up steps; the long-context workload (a step takes seconds) may run with fewer when asked to
+    warmup = max(args.warmup, 1 if args.config == "c5" else 3)
     peaks, peak_kind = load_peaks()
 
     q, k, v, dout = make_shard(cfg, rank, dev)

@@ -56,6 +56,14 @@ int rfa_version(void);
  * sequence length rounded up to a multiple of this. */
 int rfa_seq_tile(void);
 
+/*
+ * Copies the device status word to `host_copy` (one int32 of pinned host memory) in stream order, without
+ * synchronising: host_copy is set to -1 at once and holds the status word once the stream has reached the copy.
+ * The host side of this library calls it at the end of every pass and looks at the copy at the start of the next
+ * one, which is how a kernel's "bounded wait ran out" reaches the caller as an error.
+ */
+int rfa_status_publish(const int* status, int* host_copy, void* stream);
+
 /* Number of fp32 elements of the forward accumulator state for the given shape
  * (private tiled layout; allocate once per shape, opaque to the caller). */
 size_t rfa_fwd_acc_elems(int B, int Sq, int Hq, int D);

@@ -36,6 +36,7 @@ _vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_
 SIGNATURES = {
     "rfa_version": (_i, []),
     "rfa_seq_tile": (_i, []),
+    "rfa_status_publish": (_i, [_vp, _vp, _vp]),
     "rfa_fwd_acc_elems": (_sz, [_i, _i, _i, _i]),
     "rfa_dq_acc_elems": (_sz, [_i, _i, _i, _i]),
     "rfa_bwd_dq_finalize": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp]),
@@ -132,6 +133,11 @@ def _on_device(t: torch.Tensor):
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
+
+
+def status_publish(status: torch.Tensor, host_copy_ptr: int, stream=None) -> None:
+    rc = load().rfa_status_publish(_ptr(status), host_copy_ptr, _stream(stream, status))
+    _check(rc, "rfa_status_publish", kernels=0)
 
 
 def seq_tile() -> int:

@@ -50,8 +50,9 @@ int make_tmap_bshd(CUtensorMap* out, const void* base, int dtype, int B, int S, 
 
 // ----------------------------------------------------------------------------
 // Backward preprocessing: one warp per (b, s, h) row.
-//   delta = sum_d out*dout ; lse2 = lse*log2(e) ; optional clear of the fp32 dQ accumulator row.
-// Streams out, dout once (2*B*S*Hq*D*2 bytes) and writes dq_acc once: HBM-bound.
+//   delta = sum_d out*dout ; lse2 = lse*log2(e).
+// Streams out, dout once (2*B*S*Hq*D*2 bytes): HBM-bound.  (The dQ accumulator is cleared by a memset the launcher
+// enqueues in front of the kernel: a fill runs at the full write rate, a strided clear inside this kernel did not.)
 // ----------------------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ float dot8(const uint4& a, const uint4& b);
@@ -87,15 +88,8 @@ __device__ __forceinline__ float dot8<__half>(const uint4& a, const uint4& b) {
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_prepare_kernel(const T* __restrict__ out, const T* __restrict__ dout,
                                                          const float* __restrict__ lse, float* __restrict__ delta,
-                                                         float* __restrict__ lse2, float* __restrict__ dq_acc,
-                                                         size_t dq_vec4, int B, int Sq, int Spad, int Hq, int D) {
-  // clear the fp32 dQ accumulator (private tiled layout, dq_vec4 float4 elements)
-  if (dq_acc != nullptr) {
-    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < dq_vec4; i += stride)
-      reinterpret_cast<float4*>(dq_acc)[i] = z;
-  }
+                                                         float* __restrict__ lse2, int B, int Sq, int Spad, int Hq,
+                                                         int D) {
   // A row of D 16-bit values is D/8 16-byte vectors; a group of gsz lanes (gsz = 4, 8, 16 or 32, the
   // power of two >= D/8) owns one row, so a warp streams 32/gsz rows at a time with every lane loading.
   const int vec_per_row = D / 8;
@@ -283,6 +277,17 @@ extern "C" int rfa_debug_set_trace(unsigned long long* buf, int n_ctas, int cap)
 }
 extern "C" int rfa_seq_tile(void) { return 128; }
 
+extern "C" int rfa_status_publish(const int* status, int* host_copy, void* stream) {
+  if (!status || !host_copy) return RFA_ERR_INVALID_ARG;
+  *host_copy = -1;  // "not landed yet"; the copy below overwrites it with the status word in stream order
+  if (cudaMemcpyAsync(host_copy, status, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return RFA_ERR_CUDA;
+  }
+  return RFA_OK;
+}
+
 extern "C" int rfa_bwd_prepare(const void* out, const void* dout, const float* lse, float* delta, float* lse2,
                                float* dq_acc, int B, int Sq, int Hq, int D, int dtype, int* status, void* stream) {
   using namespace rfa;
@@ -300,14 +305,17 @@ extern "C" int rfa_bwd_prepare(const void* out, const void* dout, const float* l
   if (blocks > 148ll * 16) blocks = 148ll * 16;
   if (blocks < 1) blocks = 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dq_acc && cudaMemsetAsync(dq_acc, 0, dq_vec4 * sizeof(float4), s) != cudaSuccess) {
+    cudaGetLastError();
+    return RFA_ERR_CUDA;
+  }
   if (dtype == RFA_DTYPE_BF16)
     bwd_prepare_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), threads, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(dout), lse, delta, lse2, dq_acc,
-        dq_vec4, B, Sq, Spad, Hq, D);
+        static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(dout), lse, delta, lse2, B, Sq, Spad,
+        Hq, D);
   else
     bwd_prepare_kernel<__half><<<static_cast<unsigned>(blocks), threads, 0, s>>>(
-        static_cast<const __half*>(out), static_cast<const __half*>(dout), lse, delta, lse2, dq_acc, dq_vec4, B, Sq,
-        Spad, Hq, D);
+        static_cast<const __half*>(out), static_cast<const __half*>(dout), lse, delta, lse2, B, Sq, Spad, Hq, D);
   return cuda_status(cudaGetLastError());
 }
 

@@ -145,6 +145,8 @@ def test_device_status_word_surfaces_as_an_error(monkeypatch):
     once.  The failure is made on the host here (the word is written from Python, nothing faults or times out on
     the GPU): the pass that ran with the word set publishes it, and the next call on that scratch raises and
     clears it; with RFA_B200_SYNC_STATUS=1 the failing call itself raises."""
+    import time
+
     import opt_ring_flash_attn_b200 as rfa
     from opt_ring_flash_attn_b200 import workspace
 
@@ -155,6 +157,7 @@ def test_device_status_word_surfaces_as_an_error(monkeypatch):
     torch.cuda.synchronize()
     ws = workspace.forward_workspace(q, k, 1)
     ws.status.fill_(1)                       # "a pipeline wait ran out" injected from the host
+    time.sleep(0.002)                        # passes closer together than a millisecond share one status copy
     rfa.ring_flash_attn(q, k, v, causal=True)  # kernels return at once; the result of this call is invalid
     torch.cuda.synchronize()
     with pytest.raises(RuntimeError, match="device status 1"):
