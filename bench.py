@@ -26,8 +26,8 @@ Other modes
   --grid speedup     the reference harness's speed-up grid (MHA causal, D in {64,128}, H in {8,16}, S_local
                      1024..8192, warm-up 3 / 10 iterations, MAX over ranks), with and without the three input clones
                      the reference times.
-  --grid ablation    forward+backward with one host-side feature added per row: process-group transport, native
-                     transport, 16-bit dK/dV transport, zigzag layout.
+  --grid ablation    forward+backward with one host-side feature added per row: process-group transport, private
+                     NCCL transport, peer-memory transport, 16-bit dK/dV transport, zigzag layout.
 """
 from __future__ import annotations
 
@@ -473,9 +473,10 @@ def grid_mode(args, dist, dev, rank, world):
         full = [torch.randn(1, S_full, H, hd, device=dev, dtype=torch.bfloat16) for _ in range(4)]
         return [x.chunk(world, dim=1)[rank].contiguous() for x in full]
 
+    head_dims = tuple(int(x) for x in args.grid_head_dims.split(","))
     rows = []
     if args.grid == "speedup":
-        for hd in (64, 128):
+        for hd in head_dims:
             for H in (8, 16):
                 for S_local in (1024, 2048, 4096, 8192):
                     ql, kl, vl, dol = shards(hd, H, S_local)
@@ -500,11 +501,13 @@ def grid_mode(args, dist, dev, rank, world):
                                  "fwd_bwd_ms_with_clones": round(t_fc, 4), "fwd_bwd_ms": round(t_f, 4),
                                  "slowest_rank_tflops_fwd_bwd": round(3.5 * (world - 0.5) * fb / (t_f * 1e-3) / 1e12, 1)})
     else:  # ablation: forward + backward, each row adds one host-side feature
-        variants = [("A0 process-group transport", {"RFA_B200_TRANSPORT": "torch", "OPTIMIZED_RING_BWD_COMM_BF16": "0"}, False),
-                    ("A1 + native transport", {"RFA_B200_TRANSPORT": "native", "OPTIMIZED_RING_BWD_COMM_BF16": "0"}, False),
-                    ("A2 + 16-bit dK/dV transport", {"RFA_B200_TRANSPORT": "native", "OPTIMIZED_RING_BWD_COMM_BF16": "1"}, False),
-                    ("A3 + zigzag layout", {"RFA_B200_TRANSPORT": "native", "OPTIMIZED_RING_BWD_COMM_BF16": "1"}, True)]
-        for hd in (64, 128):
+        base = {"OPTIMIZED_RING_BWD_COMM_BF16": "0"}
+        variants = [("A0 process-group transport", {**base, "RFA_B200_TRANSPORT": "torch"}, False),
+                    ("A1 + private NCCL transport", {**base, "RFA_B200_TRANSPORT": "native"}, False),
+                    ("A2 + peer-memory transport", {**base, "RFA_B200_TRANSPORT": "peer"}, False),
+                    ("A3 + 16-bit dK/dV transport", {"RFA_B200_TRANSPORT": "peer", "OPTIMIZED_RING_BWD_COMM_BF16": "1"}, False),
+                    ("A4 + zigzag layout", {"RFA_B200_TRANSPORT": "peer", "OPTIMIZED_RING_BWD_COMM_BF16": "1"}, True)]
+        for hd in head_dims:
             for H in (8, 16):
                 for S_local in (2048, 4096, 8192):
                     ql, kl, vl, dol = shards(hd, H, S_local)
@@ -521,7 +524,8 @@ def grid_mode(args, dist, dev, rank, world):
 
                         row[name] = round(reference_protocol(fbw), 4)
                     rows.append(row)
-        os.environ.update({"RFA_B200_TRANSPORT": "native", "OPTIMIZED_RING_BWD_COMM_BF16": "0"})
+        os.environ.pop("RFA_B200_TRANSPORT", None)
+        os.environ["OPTIMIZED_RING_BWD_COMM_BF16"] = "0"
         schedule.shutdown()
     if rank == 0:
         print(json.dumps({"grid": args.grid, "n_gpus": world, "protocol": "warm-up 3, 10 iterations, CUDA events, MAX "
@@ -598,6 +602,7 @@ def main():
                     help="zigzag layout (rank r holds chunks r and 2W-1-r) as the timed step; not the headline config")
     ap.add_argument("--hops", action="store_true", help="add the per-hop timeline of the slowest rank")
     ap.add_argument("--grid", default=None, choices=["speedup", "ablation"])
+    ap.add_argument("--grid-head-dims", default="64,128", help="head dims of the grids, comma separated")
     ap.add_argument("--aux", action="store_true", help="time the bandwidth-bound kernels alone (1 GPU) and exit")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]

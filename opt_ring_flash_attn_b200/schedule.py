@@ -26,7 +26,7 @@ import torch
 import torch.distributed as dist
 
 from . import _native, workspace
-from .transport import PeerRingTransport, make_transport, transport_mode
+from .transport import PeerRingTransport, PeerUnavailable, make_transport, transport_mode
 
 
 # (ring key, device, ring name) -> transport.  The key is the process-group object itself (not its id(), which
@@ -66,8 +66,15 @@ def _ring_factory(group, device: torch.device):
     work on plain tensors."""
     def ring(tag: str, sizes):
         if not _is_ring_handle(group) and transport_mode(group, device) == "peer":
-            comm = PeerRingTransport(group, device, sizes)
-            return comm, comm.buffers
+            key = group if group is not None else dist.group.WORLD
+            if key not in _no_peer:
+                try:
+                    comm = PeerRingTransport(group, device, sizes)
+                    return comm, comm.buffers
+                except PeerUnavailable as e:  # the same on every rank: all fall back to the NCCL transport together
+                    _no_peer.add(key)
+                    import warnings
+                    warnings.warn(f"peer-memory ring transport unavailable, using the NCCL transport: {e}")
         return _transport(group, device, tag), [torch.empty(n, dtype=torch.uint8, device=device) for n in sizes]
     return ring
 
@@ -90,6 +97,7 @@ atexit.register(shutdown)
 
 
 _shapes_agreed = set()
+_no_peer = set()  # process groups on which the peer-memory transport could not be set up
 
 
 def _agree_on_shapes(group, q: torch.Tensor, k: torch.Tensor, W: int) -> None:

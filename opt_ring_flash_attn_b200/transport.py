@@ -151,6 +151,11 @@ class NativeRingTransport:
         return self._pending[-1]
 
 
+class PeerUnavailable(RuntimeError):
+    """The peer-memory transport could not be set up on some rank (no peer access between the GPUs, IPC refused);
+    raised on every rank of the ring alike."""
+
+
 class _DeviceMemory:
     """Lets torch wrap device memory that the transport library owns (``__cuda_array_interface__``)."""
 
@@ -176,18 +181,35 @@ class PeerRingTransport:
         self.world_size = dist.get_world_size(group)
         self.device = device
         self._handle = None
-        with torch.cuda.device(device):
-            self._handle = _native.peer_create(self.rank, self.world_size)
-            ptrs = [_native.peer_alloc(self._handle, int(n)) for n in sizes]
-            blob = _native.peer_export(self._handle)
+        self.buffers = []
+        self._pending: Deque[int] = deque()
+        # Every step that can fail on one rank only (allocation, export, mapping the neighbours) is followed by an
+        # exchange of the outcome, so that all ranks keep the transport or all ranks give it up (PeerUnavailable).
+        blob, ptrs, err = None, [], None
+        try:
+            with torch.cuda.device(device):
+                self._handle = _native.peer_create(self.rank, self.world_size)
+                ptrs = [_native.peer_alloc(self._handle, int(n)) for n in sizes]
+                blob = _native.peer_export(self._handle)
+        except RuntimeError as e:
+            err = str(e)
         blobs = [None] * self.world_size
         dist.all_gather_object(blobs, blob, group=group)
-        with torch.cuda.device(device):
-            _native.peer_connect(self._handle, blobs[(self.rank - 1) % self.world_size],
-                                 blobs[(self.rank + 1) % self.world_size])
+        if err is None and all(b is not None for b in blobs):
+            try:
+                with torch.cuda.device(device):
+                    _native.peer_connect(self._handle, blobs[(self.rank - 1) % self.world_size],
+                                         blobs[(self.rank + 1) % self.world_size])
+            except RuntimeError as e:
+                err = str(e)
+        elif err is None:
+            err = "a neighbour could not export its buffers"
+        outcomes = [None] * self.world_size
+        dist.all_gather_object(outcomes, err, group=group)  # also: every rank has mapped its neighbours before anyone posts
+        if any(o is not None for o in outcomes):
+            self.close()
+            raise PeerUnavailable("; ".join(f"rank {r}: {o}" for r, o in enumerate(outcomes) if o is not None))
         self.buffers = [torch.as_tensor(_DeviceMemory(p, int(n)), device=device) for p, n in zip(ptrs, sizes)]
-        dist.barrier(group=group)  # every rank has mapped its neighbours before anyone posts
-        self._pending: Deque[int] = deque()
         self.posted = 0
         self.bytes_sent = 0
 
