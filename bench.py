@@ -720,11 +720,11 @@ def main():
     hops = None
     if args.hops:
         sc = D ** -0.5 if scale is None else scale
-        for _ in range(2):
+        hs = ClockSampler(local_rank, period_ms=20)  # started early: nvidia-smi needs a moment to deliver samples
+        hs.start()
+        for _ in range(3):
             timeline_step(_native, schedule, group, q, k, v, dout, sc, args.zigzag)
         barrier()
-        hs = ClockSampler(local_rank, period_ms=20)
-        hs.start()
         tables = []
         for _ in range(5):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
