@@ -191,11 +191,13 @@ def _ref_worker(rank, world, port, ref_dir, steps, warmup, threads, result):
     (ring_attn.py:736-747) on its shard of the reference's CPU configuration."""
     import torch.distributed as dist
 
-    for k_ in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "GROUP_RANK", "ROLE_RANK", "LOCAL_WORLD_SIZE", "TORCHELASTIC_RUN_ID"):
-        os.environ.pop(k_, None)
-    os.environ["MASTER_ADDR"] = "127.0.0.1"
-    os.environ["MASTER_PORT"] = str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # The arm may itself run under torchrun (rank 0 of an N-GPU launch): none of the launcher's rendezvous settings
+    # may leak into these ranks (with TORCHELASTIC_USE_AGENT_STORE the env:// rendezvous expects the launcher's store).
+    for k_ in list(os.environ):
+        if k_.startswith(("TORCHELASTIC_", "TORCH_NCCL", "GROUP_", "ROLE_")) or k_ in (
+                "RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT"):
+            os.environ.pop(k_, None)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     torch.set_num_threads(threads)
     sys.path.insert(0, ref_dir)
     import ring_attn as ref  # the reference's file, unchanged
