@@ -265,7 +265,9 @@ int rfa_ring_wait(void* handle, int slot, void* compute_stream);
  *  rfa_peer_post(handle, send, recv, bytes, compute_stream) / rfa_peer_wait(handle, slot, compute_stream)
  *        as rfa_ring_post / rfa_ring_wait; send and recv must be buffers of this handle, and every rank must pass
  *        the buffer with the same number as `send` (the receiver reads it from its predecessor's memory)
- *  rfa_peer_destroy(handle)             unmaps, frees the buffers; call it on every rank before a neighbour exits
+ *  rfa_peer_destroy(handle)             unmaps, frees the buffers; call it on every rank before a neighbour exits.  It
+ *                                       waits (about two seconds at most) for the transport's stream; if that still
+ *                                       waits on a neighbour, nothing is unmapped or freed before the context goes
  * A rank that never posts leaves its neighbours' transport streams waiting (as a missing rank does to an NCCL ring).
  * Host pointers: handle, out, prev, next, ptr.
  */

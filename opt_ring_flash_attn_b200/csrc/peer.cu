@@ -20,6 +20,7 @@
 // Every rank writes before it waits, so the waits cannot form a cycle.  A peer that never posts leaves the stream
 // waiting: like an NCCL ring with a missing rank, that ends only with the process.
 #include <string.h>
+#include <time.h>
 
 #include "common.h"
 
@@ -88,8 +89,27 @@ struct PeerRing {
   bool same_peer = false;            // world size 2: previous and next rank are one process
 };
 
+// True once everything enqueued on the transport stream has run; gives up after about two seconds (a neighbour that
+// never posts leaves a wait in the stream for good).
+bool stream_drained(cudaStream_t s) {
+  for (int i = 0; i < 2000; ++i) {
+    const cudaError_t e = cudaStreamQuery(s);
+    if (e == cudaSuccess) return true;
+    if (e != cudaErrorNotReady) { cudaGetLastError(); return false; }
+    struct timespec ts = {0, 1000000};
+    nanosleep(&ts, nullptr);
+  }
+  return false;
+}
+
 void destroy_peer(PeerRing* c) {
-  if (c->stream) cudaStreamSynchronize(c->stream);
+  if (c->stream && !stream_drained(c->stream)) {
+    // The stream still waits on a neighbour: unmapping or freeing what it refers to is not safe and waiting for it
+    // could block the caller for ever (typically at process exit after another rank failed).  Leave everything to
+    // the teardown of the CUDA context.
+    delete c;
+    return;
+  }
   if (c->connected) {
     for (int i = 0; i < c->n_buffers; ++i)
       if (c->prev_buf[i]) cudaIpcCloseMemHandle(c->prev_buf[i]);

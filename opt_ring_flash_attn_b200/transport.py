@@ -16,6 +16,7 @@ until the data is actually needed.
 """
 from __future__ import annotations
 
+import time
 from collections import deque
 from typing import Deque, List, Optional
 
@@ -239,8 +240,14 @@ class PeerRingTransport:
             self._pending.clear()
             self.buffers = []
             with torch.cuda.device(self.device):
-                torch.cuda.synchronize(self.device)
-                self._native.peer_destroy(handle)
+                # the kernels that still read the buffers must have run; bounded, so that a rank whose neighbour is
+                # gone (its compute stream then waits on a transfer that never completes) can still exit
+                compute = torch.cuda.current_stream(self.device)
+                deadline = time.monotonic() + 2.0
+                while not compute.query() and time.monotonic() < deadline:
+                    time.sleep(0.001)
+                if compute.query():
+                    self._native.peer_destroy(handle)  # (itself bounded on the transport's own stream)
 
     def set_timing(self, on: bool) -> None:
         self._native.peer_timing(self._handle, on)
