@@ -18,6 +18,14 @@ extern "C" {
 int rfa_debug_mma_probe(int mode, const void* a, const void* b, float* c, int* status, void* stream);
 
 /*
+ * Launches one small kernel whose only pipeline wait can never be satisfied (an mbarrier nobody arrives on).  The
+ * bounded wait every hop kernel uses runs out after about two seconds, the kernel writes the time-out code into
+ * `status` and returns: the way to see, without any fault, what a stuck pipeline does to the status word and that the
+ * context stays usable afterwards.
+ */
+int rfa_debug_wait_timeout(int* status, void* stream);
+
+/*
  * When `buf` is non-NULL, the hop kernels launched afterwards record per-role pipeline events of their first
  * `n_ctas` CTAs into buf, laid out [n_ctas][5 roles][cap] 64-bit words (tag << 48 | SM clock; roles: 0 loader,
  * 1 MMA issuer, 2/3 elementwise groups, 4 dQ reduction).  NULL switches tracing off.  Host-side state; not

@@ -70,6 +70,7 @@ SIGNATURES = {
     "rfa_debug_peer_elapsed": (_i, [_vp, _i, ctypes.POINTER(ctypes.c_float)]),
     "rfa_debug_mma_probe": (_i, [_i, _vp, _vp, _vp, _vp, _vp]),
     "rfa_debug_set_trace": (_i, [_vp, _i, _i]),
+    "rfa_debug_wait_timeout": (_i, [_vp, _vp]),
     "rfa_debug_ring_timing": (_i, [_vp, _i]),
     "rfa_debug_ring_elapsed": (_i, [_vp, _i, ctypes.POINTER(ctypes.c_float)]),
 }
@@ -270,6 +271,13 @@ def mma_probe(mode: int, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, stat
     with _on_device(c):
         rc = load().rfa_debug_mma_probe(mode, _ptr(a), _ptr(b), _ptr(c), _ptr(status), _stream(stream, c))
     _check(rc, "rfa_debug_mma_probe")
+
+
+def wait_timeout_probe(status: torch.Tensor, stream=None) -> None:
+    """Diagnostics: a kernel whose bounded wait runs out (about two seconds); it sets ``status`` and returns."""
+    with _on_device(status):
+        rc = load().rfa_debug_wait_timeout(_ptr(status), _stream(stream, status))
+    _check(rc, "rfa_debug_wait_timeout")
 
 
 def comm_unique_id() -> bytes:

@@ -137,7 +137,30 @@ __global__ void __launch_bounds__(128, 1)
   }
 }
 
+// A wait that nothing ever satisfies: one thread waits on an mbarrier with no arrival pending.  The bounded wait of
+// tc05.cuh runs out (2 s), the CTA takes the same exit path as the hop kernels (abort flag, status word) and returns.
+__global__ void __launch_bounds__(32, 1) wait_probe_kernel(int* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (*reinterpret_cast<volatile int*>(status) != 0) return;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, &abort_flag);
+  __syncthreads();
+  if (abort_flag && threadIdx.x == 0) atomicExch(status, kStatusWaitTimeout);
+}
+
 }  // namespace rfa
+
+extern "C" int rfa_debug_wait_timeout(int* status, void* stream) {
+  if (!status) return RFA_ERR_INVALID_ARG;
+  rfa::wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status);
+  return rfa::cuda_status(cudaGetLastError());
+}
 
 extern "C" int rfa_debug_mma_probe(int mode, const void* a, const void* b, float* c, int* status, void* stream) {
   using namespace rfa;
