@@ -40,6 +40,26 @@ def deterministic(enabled: bool = True):
         _mode.deterministic = prev
 
 
+def _balanced_now() -> bool:
+    v = getattr(_mode, "balanced", None)
+    return (os.environ.get("RFA_B200_BALANCE", "0") == "1") if v is None else bool(v)
+
+
+@contextlib.contextmanager
+def balanced(enabled: bool = True):
+    """Causal calls of :func:`ring_flash_attn` on *contiguous* shards made inside this context are executed in the
+    zigzag arrangement: the shards are regrouped with one exchange of half-shards, every rank then does the same
+    amount of work (instead of (r + 1/2)/W of it on rank r), and results and gradients are regrouped back.  Same
+    call, same layout, same results to the tolerances of the operator; pays off once the ring is larger than two.
+    Needs ``S_local % 256 == 0`` (otherwise the call runs as usual).  ``RFA_B200_BALANCE=1`` sets the default."""
+    prev = getattr(_mode, "balanced", None)
+    _mode.balanced = enabled
+    try:
+        yield
+    finally:
+        _mode.balanced = prev
+
+
 def check(what: str = "ring_flash_attn") -> None:
     """Synchronise and raise ``RuntimeError`` if a kernel of any earlier call reported a failure through its device
     status word (a bounded pipeline wait that ran out).  Without this call such a failure surfaces at the start
@@ -76,12 +96,17 @@ class _RingFlashAttnFunc(torch.autograd.Function):
             assert causal, "zigzag mode requires causal=True"
         _validate(q, k, v, softmax_scale)
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        if zigzag:
+        ctx.balanced = bool(causal and not zigzag and _balanced_now() and schedule.can_balance(group, q.shape[1]))
+        if ctx.balanced:
+            out, lse, saved = schedule.balanced_forward(group, q, k, v, softmax_scale)
+            ctx.save_for_backward(*saved)  # the zigzag-arranged q, k, v, out, lse
+        elif zigzag:
             out, lse = schedule.zigzag_forward(group, q, k, v, softmax_scale)
+            ctx.save_for_backward(q, k, v, out, lse)
         else:
             out, lse = schedule.ring_forward(group, q, k, v, softmax_scale, causal)
+            ctx.save_for_backward(q, k, v, out, lse)
         ctx.zigzag = zigzag
-        ctx.save_for_backward(q, k, v, out, lse)
         ctx.softmax_scale = softmax_scale
         ctx.causal = causal
         ctx.group = group
@@ -92,7 +117,10 @@ class _RingFlashAttnFunc(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout, _dlse=None):
         q, k, v, out, lse = ctx.saved_tensors
-        if ctx.zigzag:
+        if ctx.balanced:
+            dq, dk, dv = schedule.balanced_backward(ctx.group, dout, (q, k, v, out, lse), ctx.softmax_scale,
+                                                    deterministic=ctx.deterministic)
+        elif ctx.zigzag:
             dq, dk, dv = schedule.zigzag_backward(ctx.group, dout, q, k, v, out, lse, ctx.softmax_scale,
                                                   deterministic=ctx.deterministic)
         else:

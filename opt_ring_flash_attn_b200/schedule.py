@@ -370,3 +370,96 @@ def zigzag_backward(group, dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
     _finish_dkdv(kn, final, dk, dv)
     workspace.publish_status(ws, "ring_flash_attn backward")
     return dq, dk, dv
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Balanced execution of contiguous shards
+# ----------------------------------------------------------------------------------------------------------------
+# With contiguous causal shards rank r does (r + 1/2) of W block-equivalents of work and waits for the rest of the
+# step: on 8 ranks the job runs at 8/15 of what the GPUs could do.  The zigzag layout (rank r holds chunks r and
+# 2W-1-r of 2W) gives every rank the same work.  A caller that holds contiguous shards (the reference's default
+# layout, optimized_ring_flash_attn.py:1346-1351) can still have it: the shards are regrouped into the zigzag
+# arrangement with one exchange of half-shards, the zigzag schedules run, and the results are regrouped back.  The
+# arithmetic per (query, key) pair is the same; only the rank that does it changes.
+
+def _chunk_home_contiguous(c: int) -> Tuple[int, int]:
+    """(rank, half) that holds chunk c of 2W in the contiguous layout."""
+    return c // 2, c % 2
+
+
+def _chunk_home_zigzag(c: int, W: int) -> Tuple[int, int]:
+    """(rank, half) that holds chunk c of 2W in the zigzag layout (optimized_ring_flash_attn.py:1122-1124)."""
+    return (c, 0) if c < W else (2 * W - 1 - c, 1)
+
+
+def regroup(group, tensors, to_zigzag: bool):
+    """Moves the two sequence halves of every ``[B, S_local, ...]`` tensor between the contiguous layout (rank r holds
+    chunks 2r, 2r+1) and the zigzag layout (rank r holds chunks r, 2W-1-r): one batch of point-to-point transfers of
+    half-shards on the process group (halves that stay on their rank are copied locally).  Returns new tensors."""
+    W, rank = _world(group)
+    outs = [torch.empty_like(t) for t in tensors]
+    ops, staged = [], []
+
+    def peer(r):
+        return dist.get_global_rank(group, r) if group is not None else r
+
+    for t, o in zip(tensors, outs):
+        half = t.shape[1] // 2
+        # what I hold -> where it goes
+        for h in (0, 1):
+            c = (2 * rank + h) if to_zigzag else (rank if h == 0 else 2 * W - 1 - rank)
+            dst_rank, dst_half = _chunk_home_zigzag(c, W) if to_zigzag else _chunk_home_contiguous(c)
+            src = t[:, h * half:(h + 1) * half]
+            if dst_rank == rank:
+                o[:, dst_half * half:(dst_half + 1) * half].copy_(src)
+            else:
+                buf = src.contiguous()
+                staged.append(buf)
+                ops.append(dist.P2POp(dist.isend, buf, peer(dst_rank), group=group))
+        # what I need <- where it is
+        for h in (0, 1):
+            c = (rank if h == 0 else 2 * W - 1 - rank) if to_zigzag else (2 * rank + h)
+            src_rank, _ = _chunk_home_contiguous(c) if to_zigzag else _chunk_home_zigzag(c, W)
+            if src_rank == rank:
+                continue
+            dst = o[:, h * half:(h + 1) * half]
+            if dst.is_contiguous():
+                ops.append(dist.P2POp(dist.irecv, dst, peer(src_rank), group=group))
+            else:
+                buf = torch.empty(dst.shape, dtype=dst.dtype, device=dst.device)
+                staged.append((buf, dst))
+                ops.append(dist.P2POp(dist.irecv, buf, peer(src_rank), group=group))
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    for item in staged:
+        if isinstance(item, tuple):
+            item[1].copy_(item[0])
+    return outs
+
+
+def balanced_forward(group, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float, kernels=None):
+    """Causal forward of contiguous shards, executed in the zigzag arrangement.  Returns ``(out, lse_padded, saved)``:
+    ``out`` / ``lse`` in the caller's contiguous layout, ``saved`` = the zigzag-arranged ``(q, k, v, out, lse)`` that
+    :func:`balanced_backward` needs."""
+    S = q.shape[1]
+    qz, kz, vz = regroup(group, [q, k, v], to_zigzag=True)
+    out_z, lse_z = zigzag_forward(group, qz, kz, vz, softmax_scale, kernels=kernels)
+    # lse is [B, Hq, S] (S % 256 == 0, so it carries no padding): regrouped along its last dimension
+    out, lse_t = regroup(group, [out_z, lse_z[:, :, :S].transpose(1, 2).contiguous()], to_zigzag=False)
+    return out, lse_t.transpose(1, 2).contiguous(), (qz, kz, vz, out_z, lse_z)
+
+
+def balanced_backward(group, dout: torch.Tensor, saved, softmax_scale: float, kernels=None, deterministic: bool = False):
+    qz, kz, vz, out_z, lse_z = saved
+    (dout_z,) = regroup(group, [dout.contiguous()], to_zigzag=True)
+    dq_z, dk_z, dv_z = zigzag_backward(group, dout_z, qz, kz, vz, out_z, lse_z, softmax_scale, kernels=kernels,
+                                       deterministic=deterministic)
+    dq, dk, dv = regroup(group, [dq_z, dk_z, dv_z], to_zigzag=False)
+    return dq, dk, dv
+
+
+def can_balance(group, S_local: int) -> bool:
+    """Balanced execution needs a ring of at least two ranks and half-shards that are whole 128-row tiles."""
+    W, _ = _world(group)
+    return W > 1 and S_local % 256 == 0 and not _is_ring_handle(group)

@@ -33,7 +33,9 @@ def _worker(rank, world, port, cfg, errs, transport):
 
         B, S, Hq, Hkv, D, causal, dtype = cfg[:7]
         os.environ["RFA_B200_TRANSPORT"] = transport
-        zigzag = len(cfg) > 7 and cfg[7]
+        zigzag = len(cfg) > 7 and cfg[7] is True
+        balance = len(cfg) > 7 and cfg[7] == "balanced"  # contiguous shards, executed in the zigzag arrangement
+        os.environ["RFA_B200_BALANCE"] = "1" if balance else "0"
         wire16 = len(cfg) > 8 and cfg[8]  # dK/dV travel in the input dtype (the reference's OPTIMIZED_RING_BWD_COMM_BF16)
         os.environ["OPTIMIZED_RING_BWD_COMM_BF16"] = "1" if wire16 else "0"
         q, k, v, dout = (x.to(dev) for x in make_inputs(60, B, S * world, Hq, Hkv, D, dtype=dtype))
@@ -82,6 +84,7 @@ def _worker(rank, world, port, cfg, errs, transport):
     (1, 320, 2, 2, 256, True, torch.bfloat16),
     (1, 512, 4, 2, 128, True, torch.bfloat16, True),  # zigzag layout
     (1, 384, 4, 2, 128, True, torch.bfloat16, False, True),  # 16-bit dK/dV transport
+    (2, 512, 4, 2, 128, True, torch.bfloat16, "balanced"),  # contiguous shards regrouped internally (B = 2: strided halves)
 ])
 @pytest.mark.parametrize("transport", ["peer", "native"])
 def test_ring_nccl(cfg, transport):

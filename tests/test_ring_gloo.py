@@ -172,3 +172,68 @@ def test_transport_rejects_same_buffer_and_unposted_wait():
             t.post(buf, buf)
     finally:
         dist.destroy_process_group()
+
+
+def _balanced_worker(rank, world, port, Hq, Hkv, errs):
+    os.environ["OPTIMIZED_RING_BWD_COMM_BF16"] = "0"
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    try:
+        import sys
+        sys.path.insert(0, os.path.dirname(__file__))
+        import fake_kernels
+        from opt_ring_flash_attn_b200 import schedule
+        from oracle.ring_attn_oracle import zigzag_shard
+
+        B, S, D = 2, 256, 16  # two 128-row halves per rank; B = 2 makes the half-shard views non-contiguous
+        q, k, v, dout = make_inputs(72, B, S * world, Hq, Hkv, D, dtype=torch.bfloat16)
+        qs, ks, vs, dos = shard(q, world), shard(k, world), shard(v, world), shard(dout, world)
+        # the regrouping alone: contiguous -> zigzag gives the zigzag shards, and back is the identity
+        (qz,) = schedule.regroup(None, [qs[rank]], to_zigzag=True)
+        assert torch.equal(qz, zigzag_shard(q, world)[rank])
+        (qc,) = schedule.regroup(None, [qz], to_zigzag=False)
+        assert torch.equal(qc, qs[rank])
+        scale = 0.25
+        assert schedule.can_balance(None, S)
+        out, lse, saved = schedule.balanced_forward(None, qs[rank], ks[rank], vs[rank], scale, kernels=fake_kernels)
+        dq, dk, dv = schedule.balanced_backward(None, dos[rank], saved, scale, kernels=fake_kernels)
+        ref = ring_attn_oracle(qs, ks, vs, dos, causal=True, softmax_scale=scale)  # contiguous layout
+
+        def rel(a, b):
+            return ((a.float() - b).norm() / b.norm()).item()
+
+        assert (out.float() - ref["out"][rank]).abs().max().item() <= 1e-2
+        assert (lse[:, :, :S] - ref["lse"][rank]).abs().max().item() <= 1e-3
+        assert rel(dq, ref["dq"][rank]) <= 2e-2, rel(dq, ref["dq"][rank])
+        assert rel(dk, ref["dk"][rank]) <= 2e-2, rel(dk, ref["dk"][rank])
+        assert rel(dv, ref["dv"][rank]) <= 2e-2, rel(dv, ref["dv"][rank])
+        dist.barrier()
+    except Exception as e:
+        errs.put(f"rank {rank}: {type(e).__name__}: {e}")
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,Hq,Hkv", [(2, 2, 2), (3, 4, 2), (4, 2, 1)])
+def test_balanced_execution_of_contiguous_shards_on_gloo(world, Hq, Hkv):
+    """Contiguous shards regrouped to the zigzag arrangement, zigzag schedules, results regrouped back: every rank
+    must get the contiguous-layout results of the oracle (odd world sizes send both halves of one rank to one peer)."""
+    ctx = mp.get_context("spawn")
+    errs = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_balanced_worker, args=(r, world, port, Hq, Hkv, errs)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+    msgs = []
+    while not errs.empty():
+        msgs.append(errs.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            msgs.append("a rank did not finish in time")
+    assert not msgs and all(p.exitcode == 0 for p in procs), msgs
